@@ -2,8 +2,9 @@
 the function that lays the model out from that configuration.
 
 The reference has no registry: it accepts ``model_type == "qwen3"`` and nothing
-else (src/engine.rs:24-29).  Here config.json's ``architectures[0]`` chooses the
-entry and ``model_type`` is the fallback, so that another architecture is one
+else (src/engine.rs:24-29).  Here config.json's ``architectures[0]`` (or its
+``architecture``, where a file names one design) chooses the entry and
+``model_type`` is the fallback, so that another architecture is one
 ``register_architecture`` call away and no caller names a model class.
 """
 from __future__ import annotations
@@ -46,6 +47,8 @@ def resolve_architecture(raw: dict, where: str = "config.json") -> Architecture:
     names = raw.get("architectures") or []
     if isinstance(names, str):
         names = [names]
+    if isinstance(raw.get("architecture"), str):     # a file that names one design
+        names = list(names) + [raw["architecture"]]
     for n in names:
         if n in _BY_NAME:
             return _BY_NAME[n]

@@ -9,7 +9,9 @@
 // the other sequences of the batch, or where its pages lie.
 // Scores are q.k * scale; key j is visible when j <= pos and, with a window W,
 // when j > pos - W (the reference masks with -1e30 instead of skipping,
-// src/kernels.rs:1190-1191, 1256; same result).
+// src/kernels.rs:1190-1191, 1256; same result).  With a cap c > 0 a score s
+// becomes c * tanh(s / c); with sinks, exp(sinks[h]) is one more term of query
+// head h's denominator, without a value.
 #include "common.cuh"
 
 #define ATT_THREADS 128
@@ -22,7 +24,8 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
                                     const int* __restrict__ token_seq,
                                     const int* __restrict__ token_pos,
                                     const int* __restrict__ slots, T* __restrict__ out, int nq,
-                                    int nkv, int D, int page, float scale, int window) {
+                                    int nkv, int D, int page, float scale, int window,
+                                    float softcap, const float* __restrict__ sinks) {
   extern __shared__ float sm[];
   __shared__ float scratch[32];
   float* q_s = sm;       // [D]
@@ -56,6 +59,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
       float a = 0.f;
       for (int d = 0; d < D; ++d) a = fmaf(q_s[d], to_f32<T>(kr[d]), a);
       s = a * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float cmax = block_max(s, scratch);  // key c is always valid, so finite
     const float m_new = fmaxf(m, cmax);
@@ -79,6 +83,14 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, const T* __restrict
     m = m_new;
     __syncthreads();  // p_s is rewritten by the next chunk
   }
+  if (sinks) {   // one more term of the denominator; it may be the largest
+    const float sk = sinks[h];
+    const float m_new = fmaxf(m, sk);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_ACC; ++i) acc[i] *= corr;
+  }
   const float inv_l = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_ACC; ++i) {
@@ -91,7 +103,7 @@ template <typename T>
 static int launch(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                   int max_pages, const int* token_seq, const int* token_pos, const int* slots,
                   void* out, int n_tokens, int nq, int nkv, int D, int page, float scale,
-                  int window, cudaStream_t stream) {
+                  int window, float softcap, const float* sinks, cudaStream_t stream) {
   if (n_tokens < 0 || nq <= 0 || nkv <= 0 || nq % nkv || D <= 0 || page <= 0 || max_pages <= 0)
     return GB_ERR_BAD_ARG;
   if (D > ATT_THREADS * ATT_MAX_ACC) return GB_ERR_UNSUPPORTED;
@@ -99,7 +111,7 @@ static int launch(const void* q, const void* k_pages, const void* v_pages, const
   const size_t smem = (size_t)(D + ATT_THREADS) * sizeof(float);
   attn_generic_kernel<T><<<dim3(n_tokens, nq), ATT_THREADS, smem, stream>>>(
       (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, token_seq,
-      token_pos, slots, (T*)out, nq, nkv, D, page, scale, window);
+      token_pos, slots, (T*)out, nq, nkv, D, page, scale, window, softcap, sinks);
   return gb_status();
 }
 
@@ -107,15 +119,15 @@ GB_EXPORT int gb_attn_generic_f32(const void* q, const void* k_pages, const void
                                   const int* block_table, int max_pages, const int* token_seq,
                                   const int* token_pos, const int* slots, void* out, int n_tokens,
                                   int nq, int nkv, int D, int page, float scale, int window,
-                                  cudaStream_t s) {
+                                  float softcap, const float* sinks, cudaStream_t s) {
   return launch<float>(q, k_pages, v_pages, block_table, max_pages, token_seq, token_pos, slots,
-                       out, n_tokens, nq, nkv, D, page, scale, window, s);
+                       out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, s);
 }
 GB_EXPORT int gb_attn_generic_bf16(const void* q, const void* k_pages, const void* v_pages,
                                    const int* block_table, int max_pages, const int* token_seq,
                                    const int* token_pos, const int* slots, void* out, int n_tokens,
                                    int nq, int nkv, int D, int page, float scale, int window,
-                                   cudaStream_t s) {
+                                   float softcap, const float* sinks, cudaStream_t s) {
   return launch<bf16>(q, k_pages, v_pages, block_table, max_pages, token_seq, token_pos, slots,
-                      out, n_tokens, nq, nkv, D, page, scale, window, s);
+                      out, n_tokens, nq, nkv, D, page, scale, window, softcap, sinks, s);
 }

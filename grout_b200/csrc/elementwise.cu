@@ -120,3 +120,67 @@ GB_EXPORT int gb_delay_ns(long long ns, cudaStream_t s) {
   delay_kernel<<<1, 1, 0, s>>>((unsigned long long)ns);
   return gb_status();
 }
+
+// out[i] = max(in[i], 0)^2: the activation of a feed-forward without a gate.  The
+// square is taken in 32-bit and rounded once.
+template <typename T>
+__global__ void relu_squared_kernel(const T* in, T* __restrict__ out, size_t n) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = fmaxf(to_f32<T>(in[i]), 0.f);
+  pdl_launch_dependents_if_large();
+  out[i] = from_f32<T>(v * v);
+}
+__global__ void relu_squared_vec8_kernel(const bf16* in, bf16* __restrict__ out, size_t n8) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 x4 = reinterpret_cast<const uint4*>(in)[i];
+  pdl_launch_dependents_if_large();
+  const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x4);
+  uint4 o4;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float a = fmaxf(__low2float(x2[k]), 0.f), b = fmaxf(__high2float(x2[k]), 0.f);
+    o2[k] = __floats2bfloat162_rn(a * a, b * b);
+  }
+  reinterpret_cast<uint4*>(out)[i] = o4;
+}
+template <typename T>
+static int relu_squared(const void* in, void* out, long long n, cudaStream_t s) {
+  if (n < 0 || !in || !out) return GB_ERR_BAD_ARG;
+  if (n == 0) return 0;
+  if (sizeof(T) == 2 && n % 8 == 0 && ((((uintptr_t)in) | ((uintptr_t)out)) & 15) == 0)
+    return gb_launch(relu_squared_vec8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, s,
+                     (const bf16*)in, (bf16*)out, (size_t)(n / 8));
+  return gb_launch(relu_squared_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s,
+                   (const T*)in, (T*)out, (size_t)n);
+}
+GB_EXPORT int gb_relu_squared_f32(const void* in, void* out, long long n, cudaStream_t s) {
+  return relu_squared<float>(in, out, n, s);
+}
+GB_EXPORT int gb_relu_squared_bf16(const void* in, void* out, long long n, cudaStream_t s) {
+  return relu_squared<bf16>(in, out, n, s);
+}
+
+// x[i] <- cap * tanh(x[i] * scale / cap) in place on 32-bit values (cap <= 0: only
+// the scaling): what an output head with a scaled and capped logit does.
+__global__ void scale_softcap_kernel(float* x, size_t n, float scale, float cap) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i] * scale;
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  x[i] = v;
+}
+GB_EXPORT int gb_scale_softcap_f32(float* x, long long n, float scale, float cap, cudaStream_t s) {
+  if (n < 0 || !x) return GB_ERR_BAD_ARG;
+  if (n == 0) return 0;
+  return gb_launch(scale_softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, x,
+                   (size_t)n, scale, cap);
+}

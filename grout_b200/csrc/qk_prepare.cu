@@ -26,6 +26,7 @@ struct QkPrepareArgs {
   const float* qkv_parts;   // instead of qkv: n_parts 32-bit partial sums of it, added in order
   int n_parts;              //   (the split-K projection leaves its reduction to this kernel)
   long long part_stride;    //   floats between partials
+  int v_from_k;             // the projection has no v: a value is its key before the rotation
 };
 
 template <typename T, typename WT>
@@ -35,7 +36,7 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
-  const int n_heads = a.nq + 2 * a.nkv;
+  const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
   if (head >= n_heads) return;  // warps are independent below
   const int D = a.D;
@@ -64,6 +65,21 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
     __syncwarp();
   }
   const int pos = a.token_pos[t];
+  if (kind == 1 && a.v_from_k) {   // the value: the key as it stands now
+    const int hh = head - a.nq;
+    if (a.kv_out) {
+      T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + a.nkv + hh) * D;
+      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+    }
+    if (a.k_pages) {
+      const int slot = a.slots[a.token_seq[t]];
+      if (slot >= 0) {
+        T* dst = (T*)a.v_pages +
+                 paged_row(a.block_table + (size_t)slot * a.max_pages, pos, hh, a.nkv, a.page, D);
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+      }
+    }
+  }
   if (kind != 2 && a.inv_freq) {
     const int half = a.rot_dim / 2;
     for (int j = lane; j < half; j += 32) {
@@ -420,13 +436,14 @@ static int launch_fast(const QkPrepareArgs& a, cudaStream_t stream) {
 }
 
 static bool fast_ok(const QkPrepareArgs& a) {
-  return (a.D == 64 || a.D == 128 || a.D == 256) && (!a.inv_freq || a.rot_dim == a.D);
+  return (a.D == 64 || a.D == 128 || a.D == 256) && (!a.inv_freq || a.rot_dim == a.D) &&
+         !a.v_from_k;
 }
 
 template <typename T, typename WT>
 static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
-  const int n_heads = a.nq + 2 * a.nkv;
+  const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
   dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
   const size_t smem = (size_t)warps * a.D * sizeof(float);
   if (smem > 48 * 1024) return GB_ERR_UNSUPPORTED;
@@ -443,6 +460,7 @@ static int check(const QkPrepareArgs& a) {
                     a.max_pages <= 0))
     return GB_ERR_BAD_ARG;
   if (!a.token_pos) return GB_ERR_BAD_ARG;
+  if (a.v_from_k && (a.k_w || a.nkv <= 0)) return GB_ERR_UNSUPPORTED;
   return 0;
 }
 

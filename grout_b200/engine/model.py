@@ -11,6 +11,7 @@ import torch
 
 from ..cache import CacheLayout, SequenceCache
 from ..parts.base import BuildContext, ParamSpec, Part, build_part
+from ..parts.norm import with_offset
 from ..parts.plan import ModelPlan
 from .batch import StepContext
 
@@ -30,6 +31,7 @@ class Model:
         self.final_norm = build_part("norm", plan.final_norm, ctx)
         self.head = build_part("head", plan.head, ctx)
         self._layout: Optional[CacheLayout] = None
+        self.stream_vectors: Dict[str, torch.Tensor] = {}    # 32-bit [rows, hidden] each
 
     # -- tensors -----------------------------------------------------------
     def _named_parts(self) -> List[Tuple[str, Part]]:
@@ -52,6 +54,12 @@ class Model:
                 if name in exp:
                     raise ValueError(f"two parts read tensor '{name}'")
                 exp[name] = spec
+        for name, shape in self.plan.stream_vectors:
+            if name in exp:
+                raise ValueError(f"two parts read tensor '{name}'")
+            exp[name] = ParamSpec(tuple(shape), "offset")
+        for name, shape in self.plan.unread_tensors:
+            exp.setdefault(name, ParamSpec(tuple(shape), "vector", optional=True))
         return exp
 
     def load(self, get: Callable[[str], torch.Tensor]) -> None:
@@ -62,6 +70,8 @@ class Model:
                 part.load({local: get(prefix + local) for local in specs})
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding.weight)
+        for name, _shape in self.plan.stream_vectors:     # added in 32-bit, as the stream is
+            self.stream_vectors[name] = get(name).float().contiguous()
 
     # -- cache -------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:
@@ -95,6 +105,8 @@ class Model:
         for i, e in enumerate(self.plan.schedule):
             owner = i if e.cache_of is None else e.cache_of
             view = cache.view(owner) if owner in layout.where else None
+            if e.add is not None:
+                pending = with_offset(pending, self.stream_vectors[e.add[0]][e.add[1]])
             res, pending = self.blocks[e.layer].forward(res, pending, step, view)
         if step.n_want == 0:
             return None

@@ -298,6 +298,78 @@ def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
     return res_out, y
 
 
+class _LayerNormArgs(ctypes.Structure):
+    _fields_ = [("res_in", _P), ("delta", _P), ("parts", _P), ("n_parts", _I), ("part_stride", _L),
+                ("rows", _P), ("post_w", _P), ("post_b", _P), ("post_eps", _F), ("post_center", _I),
+                ("mult", _F), ("offset", _P), ("w", _P), ("b", _P), ("eps", _F), ("center", _I),
+                ("res_out", _P), ("y", _P), ("n_rows", _I), ("N", _I)]
+
+
+@_profiled("add_layernorm", _cost_io)
+def add_layernorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
+                  weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+                  center: bool = True, *, dtype: torch.dtype,
+                  rows: Optional[torch.Tensor] = None, write_res: bool = True, mult: float = 1.0,
+                  offset: Optional[torch.Tensor] = None, post_weight: Optional[torch.Tensor] = None,
+                  post_bias: Optional[torch.Tensor] = None, post_eps: float = 0.0,
+                  post_center: bool = True) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """v = res_in + mult * post(delta) + offset in 32-bit -> (residual, norm(v)).
+
+    ``post`` is the layer norm (post_weight, post_bias, post_eps) that ``delta``
+    passes through first, the identity without ``post_weight``; ``norm`` is the
+    layer norm (weight, bias, eps), and without ``weight`` only the sum is made.
+    A norm that does not ``center`` leaves the mean in.  ``delta`` is [T, N] in
+    ``dtype`` or a stack of 32-bit partial sums [S, T, N], added in order;
+    ``offset`` is a 32-bit vector [N]; norm weights and biases are 32-bit.  Without
+    ``rows`` the residual is updated in place when ``res_in`` is given."""
+    parts = None
+    if delta is not None and delta.dim() == 3:
+        _need(delta, "partial sums", torch.float32, 3)
+        parts, delta = delta, None
+    src = res_in if res_in is not None else (delta if delta is not None else
+                                             (parts[0] if parts is not None else None))
+    if src is None:
+        raise KernelError("add_layernorm needs a residual or a delta")
+    if res_in is not None:
+        _need(res_in, "residual", torch.float32, 2)
+    if delta is not None:
+        _need(delta, "delta", dtype, 2)
+        if res_in is not None and delta.shape != res_in.shape:
+            raise KernelError(f"residual {tuple(res_in.shape)} and delta {tuple(delta.shape)} differ")
+    if parts is not None and res_in is not None and tuple(parts.shape[1:]) != tuple(res_in.shape):
+        raise KernelError(f"residual {tuple(res_in.shape)} and partial sums {tuple(parts.shape)} differ")
+    N = src.shape[1]
+    for t, nm in ((weight, "norm weight"), (bias, "norm bias"), (post_weight, "inner norm weight"),
+                  (post_bias, "inner norm bias"), (offset, "offset")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.shape[0] != N:
+                raise KernelError(f"{nm} has {t.shape[0]} elements for rows of {N}")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+        n_rows = rows.shape[0]
+    else:
+        n_rows = src.shape[0]
+    res_out = None
+    if write_res or weight is None:
+        if rows is None and res_in is not None:
+            res_out = res_in
+        else:
+            res_out = torch.empty((n_rows, N), dtype=torch.float32, device=src.device)
+    y = torch.empty((n_rows, N), dtype=dtype, device=src.device) if weight is not None else None
+    a = _LayerNormArgs()
+    a.res_in, a.delta, a.parts = _ptr(res_in), _ptr(delta), _ptr(parts)
+    a.n_parts = 0 if parts is None else parts.shape[0]
+    a.part_stride = 0 if parts is None else parts.stride(0)
+    a.rows, a.post_w, a.post_b = _ptr(rows), _ptr(post_weight), _ptr(post_bias)
+    a.post_eps, a.post_center, a.mult, a.offset = float(post_eps), int(post_center), float(mult), _ptr(offset)
+    a.w, a.b, a.eps, a.center = _ptr(weight), _ptr(bias), float(eps), int(center)
+    a.res_out, a.y, a.n_rows, a.N = _ptr(res_out), _ptr(y), n_rows, N
+    _check(_fn("layernorm", f"gb_add_layernorm_{_suffix(dtype)}", "pp")(
+        ctypes.addressof(a), _stream()), "add_layernorm")
+    return res_out, y
+
+
 # ---------------------------------------------------------------- q/k preparation
 class _QkPrepareArgs(ctypes.Structure):
     _fields_ = [("qkv", _P), ("q_w", _P), ("k_w", _P), ("inv_freq", _P), ("token_seq", _P),
@@ -305,17 +377,18 @@ class _QkPrepareArgs(ctypes.Structure):
                 ("kv_out", _P), ("k_pages", _P), ("v_pages", _P), ("eps", _F),
                 ("n_tokens", _I), ("nq", _I), ("nkv", _I), ("D", _I), ("rot_dim", _I),
                 ("max_pages", _I), ("page", _I), ("qkv_parts", _P), ("n_parts", _I),
-                ("part_stride", _L)]
+                ("part_stride", _L), ("v_from_k", _I)]
 
 
 @_profiled("qk_prepare", lambda out, qkv, nq, nkv, D, **k: _cost_qk_prepare(out, qkv, nq, nkv, D))
 def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=None,
                eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
                block_table=None, k_pages=None, v_pages=None, page: int = 0,
-               want_kv_out: bool = False):
+               want_kv_out: bool = False, values_are_keys: bool = False):
     """Returns (q [T, nq, D], kv_out or None); writes k, v into the pages when given.
     ``qkv`` may be a stack of 32-bit partial sums [S, T, width] of the projection
-    (bf16 engines only): they are added in order."""
+    (bf16 engines only): they are added in order.  ``values_are_keys``: the
+    projection holds q and k only, and a value is its key before the rotation."""
     parts = None
     if qkv.dim() == 3:
         _need(qkv, "qkv partial sums", torch.float32, 3)
@@ -326,9 +399,10 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
         _need(qkv, "qkv", ndim=2)
         dt = qkv.dtype
     T = qkv.shape[-2]
-    if qkv.shape[-1] != (nq + 2 * nkv) * D:
-        raise KernelError(f"qkv has {qkv.shape[-1]} columns, expected (nq + 2 nkv) * D = "
-                          f"{(nq + 2 * nkv) * D}")
+    n_in = nq + (nkv if values_are_keys else 2 * nkv)
+    if qkv.shape[-1] != n_in * D:
+        raise KernelError(f"the projection has {qkv.shape[-1]} columns, expected {n_in} heads of "
+                          f"{D} = {n_in * D}")
     w_is_f32 = int(dt == torch.float32)      # without norm weights: whatever the entry point takes
     for w, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
         if w is not None:
@@ -355,6 +429,7 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     a.token_seq, a.token_pos, a.slots = token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr()
     a.q_out, a.kv_out = q.data_ptr(), _ptr(kv_out)
     a.eps, a.n_tokens, a.nq, a.nkv, a.D, a.rot_dim = float(eps), T, nq, nkv, D, int(rot_dim)
+    a.v_from_k = int(values_are_keys)
     if k_pages is not None:
         _need(k_pages, "k pages", dt, 4)
         _need(v_pages, "v pages", dt, 4)
@@ -403,17 +478,26 @@ def _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, 
     return T, nq, nkv, D
 
 
+def _check_sinks(sinks, nq: int) -> None:
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != nq:
+            raise KernelError(f"{sinks.shape[0]} sinks for {nq} query heads")
+
+
 @_profiled("attn_generic", lambda out, q, *a, **k: (_nbytes(q, out), 0))
 def attn_generic(q, k_pages, v_pages, block_table, *, token_seq, token_pos, slots, page: int,
-                 scale: float, window: Optional[int] = None) -> torch.Tensor:
+                 scale: float, window: Optional[int] = None, softcap: Optional[float] = None,
+                 sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     T, nq, nkv, D = _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, page)
+    _check_sinks(sinks, nq)
     out = torch.empty_like(q)
     sfx = _suffix(q.dtype)
-    _check(_fn("attn_generic", f"gb_attn_generic_{sfx}", "ppppippppiiiiifip")(
+    _check(_fn("attn_generic", f"gb_attn_generic_{sfx}", "ppppippppiiiiififpp")(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr(),
-        out.data_ptr(), T, nq, nkv, D, page, float(scale), int(window or 0), _stream()),
-        "attn_generic")
+        out.data_ptr(), T, nq, nkv, D, page, float(scale), int(window or 0), float(softcap or 0.0),
+        _ptr(sinks), _stream()), "attn_generic")
     return out
 
 
@@ -447,6 +531,25 @@ def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     _check(_fn("elementwise", f"gb_silu_mul_{sfx}", "ppiiip")(
         gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "silu_mul")
     return out
+
+
+@_profiled("relu_squared", _cost_io)
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2, squared in 32-bit."""
+    _need(x, "tensor")
+    out = torch.empty_like(x)
+    _check(_fn("elementwise", f"gb_relu_squared_{_suffix(x.dtype)}", "pplp")(
+        x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "relu_squared")
+    return out
+
+
+@_profiled("scale_softcap", lambda out, x, *a: (2 * _nbytes(x), 0))
+def scale_softcap_(x: torch.Tensor, scale: float, cap: Optional[float]) -> torch.Tensor:
+    """x <- cap * tanh(x * scale / cap) in place on 32-bit values (no cap: x * scale)."""
+    _need(x, "tensor", torch.float32)
+    _check(_fn("elementwise", "gb_scale_softcap_f32", "plffp")(
+        x.data_ptr(), x.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return x
 
 
 @_profiled("cast", lambda out, x, dtype: ((0, 0) if out is x else (_nbytes(x, out), 0)))
@@ -1050,12 +1153,17 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
 
 # ---------------------------------------------------------------- attention dispatch
 def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float,
-              window: Optional[int] = None) -> torch.Tensor:
+              window: Optional[int] = None, softcap: Optional[float] = None,
+              sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's queries over their sequences' cached keys.
     32-bit tensors take the plain 32-bit kernel; bfloat16 takes the tensor-core
-    kernels where they accept the shape and the plain kernel elsewhere."""
+    kernels where they accept the shape and the plain kernel elsewhere.
+    ``softcap`` c: scores become c * tanh(score / c); ``sinks`` [nq] float32: one
+    more term exp(sinks[h]) in the denominator of query head h."""
     _T, nq, D = q.shape
-    if q.dtype == torch.bfloat16 and fast_attention_takes(D, nq, k_pages.shape[1], page):
+    plain_only = bool(softcap) or sinks is not None
+    if q.dtype == torch.bfloat16 and not plain_only and \
+            fast_attention_takes(D, nq, k_pages.shape[1], page):
         nkv = k_pages.shape[1]
         if step.decode and attn_decode_tma_takes(D, nq, nkv, page) and (
                 DECODE_ATTENTION == "tma" or
@@ -1078,7 +1186,7 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
                                  page=page, scale=scale, window=window)
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
-                        window=window)
+                        window=window, softcap=softcap, sinks=sinks)
 
 
 # ---------------------------------------------------------------- sampling

@@ -1,16 +1,17 @@
 from .base import (BuildContext, ParamSpec, Part, PartSpec, ProductChoice, build_part,
                    known_parts, register_part, unregister_part)
-from .block import Block, PreNormBlock
-from .feedforward import FeedForward, SwiGLU
+from .block import Block, PreNormBlock, SandwichBlock
+from .feedforward import FeedForward, ReluSquaredMLP, SwiGLU
 from .io import Embedding, Head, LinearHead, TokenEmbedding
 from .linear import Linear
 from .mixer import GQAAttention, Mixer
-from .norm import Norm, RMSNorm, residual_add
+from .norm import Contribution, LayerNorm, Norm, RMSNorm, residual_add
 from .plan import LayerPlan, ModelPlan, ScheduleEntry
 from .position import NoPosition, PositionEncoding, RotaryHalfSplit, RotaryTable
 
 __all__ = ["BuildContext", "ParamSpec", "Part", "PartSpec", "ProductChoice", "build_part", "known_parts",
-           "register_part", "unregister_part", "Block", "PreNormBlock", "FeedForward", "SwiGLU",
+           "register_part", "unregister_part", "Block", "PreNormBlock", "SandwichBlock", "FeedForward", "ReluSquaredMLP", "SwiGLU",
+           "Contribution", "LayerNorm",
            "Embedding", "Head", "LinearHead", "TokenEmbedding", "Linear", "GQAAttention", "Mixer",
            "Norm", "RMSNorm", "residual_add", "LayerPlan", "ModelPlan", "ScheduleEntry",
            "NoPosition", "PositionEncoding", "RotaryHalfSplit", "RotaryTable"]

@@ -22,8 +22,9 @@ import torch
 class ParamSpec:
     """One tensor that a part reads from the checkpoint.
 
-    kind: "matrix" (a linear or embedding weight), "vector" (norm weights,
-    biases and other small tensors) or "table" (integer tables, kept as int32).
+    kind: "matrix" (a linear or embedding weight), "vector" (norm weights and
+    other small tensors around one), "offset" (biases and other small tensors
+    around zero) or "table" (integer tables, kept as int32).
     The loader keeps bfloat16 as bfloat16 and 32-bit as 32-bit for every kind;
     only the true 32-bit path widens, and only half precision is converted.
     """

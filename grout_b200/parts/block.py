@@ -12,7 +12,10 @@ from __future__ import annotations
 
 from typing import Dict
 
+from typing import Optional
+
 from .base import BuildContext, Part, PartSpec, build_part, register_part
+from .norm import Contribution
 
 
 class Block(Part):
@@ -56,3 +59,51 @@ class PreNormBlock(Block):
         a = self.mixer.forward(n, step, cache)
         res, m = self.norm2.add_norm(res, a)
         return res, self.feedforward.forward(m, step)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    """A norm in front of every sublayer and another behind it, whose output
+    enters the stream times ``mult``:
+
+        x += mult * norm1b(mixer(norm1(x)));  x += mult * norm2b(feedforward(norm2(x)))
+
+    The second line is absent when the layer has no feed-forward.  A sublayer's
+    output leaves here as a ``Contribution`` (its norm and factor still to be
+    applied), so the norm that reads the stream next does the normalising, the
+    scaling, the 32-bit sum and its own normalising in one kernel."""
+
+    def __init__(self, ctx: BuildContext, norm1: PartSpec, mixer: PartSpec, norm1b: PartSpec,
+                 norm2: Optional[PartSpec] = None, feedforward: Optional[PartSpec] = None,
+                 norm2b: Optional[PartSpec] = None, mult: float = 1.0):
+        super().__init__(ctx)
+        if (feedforward is None) != (norm2 is None) or (feedforward is None) != (norm2b is None):
+            raise ValueError("a feed-forward comes with both of its norms, or none of the three")
+        self.mult = float(mult)
+        self.norm1 = build_part("norm", norm1, ctx)
+        self.mixer = build_part("mixer", mixer, ctx)
+        self.norm1b = build_part("norm", norm1b, ctx)
+        self.norm2 = build_part("norm", norm2, ctx) if norm2 else None
+        self.feedforward = build_part("feedforward", feedforward, ctx) if feedforward else None
+        self.norm2b = build_part("norm", norm2b, ctx) if norm2b else None
+
+    def named_parts(self) -> Dict[str, Part]:
+        roles = ("norm1", "mixer", "norm1b", "norm2", "feedforward", "norm2b")
+        return {r: getattr(self, r) for r in roles if getattr(self, r) is not None}
+
+    def children(self):
+        return tuple(self.named_parts().values())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, res, pending, step, cache):
+        res, n = self.norm1.add_norm(res, pending)
+        a = Contribution(self.mixer.forward(n, step, cache), self.norm1b, self.mult)
+        if self.feedforward is None:
+            return res, a
+        res, m = self.norm2.add_norm(res, a)
+        return res, Contribution(self.feedforward.forward(m, step), self.norm2b, self.mult)

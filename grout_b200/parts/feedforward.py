@@ -59,3 +59,34 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, step):
         return self.down(self.gate_up.silu_mul(x, self.interleave), partial_ok=True)
+
+
+@register_part("feedforward", "relu2_mlp")
+class ReluSquaredMLP(FeedForward):
+    """d = (max(x Wu^T, 0))^2 Wd^T, no biases, no gate.  The square of the relu
+    is taken in 32-bit on the product's accumulator where the product's kernel
+    has that epilogue, else by a kernel of its own.  ``names``: the local names of
+    the two tensors (keys up, down)."""
+
+    def __init__(self, ctx: BuildContext, hidden: int, intermediate: int, names=None):
+        super().__init__(ctx)
+        self.hidden, self.intermediate = int(hidden), int(intermediate)
+        self.names = dict({"up": "up_proj.weight", "down": "down_proj.weight"}, **(names or {}))
+        self.up = self.down = None
+
+    def param_specs(self):
+        return {self.names["up"]: ParamSpec((self.intermediate, self.hidden)),
+                self.names["down"]: ParamSpec((self.hidden, self.intermediate))}
+
+    def load(self, params):
+        self.up = Linear(params[self.names["up"]], self.ctx.products)
+        self.down = Linear(params[self.names["down"]], self.ctx.products)
+
+    def kernel_modules(self):
+        return ("elementwise",) + self.up.kernel_modules() + self.down.kernel_modules()
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step):
+        return self.down(self.up.relu_squared(x), partial_ok=True)

@@ -101,3 +101,7 @@ class Linear:
                       ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True)))):
             return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)
+
+    def relu_squared(self, x: torch.Tensor) -> torch.Tensor:
+        """max(x W^T, 0)^2, squared before the rounding to the compute dtype."""
+        return ops.relu_squared(self(x))

@@ -50,12 +50,25 @@ class GQAAttention(Mixer):
     scale = 1/sqrt(head_dim) unless given (src/model.rs:2398); query head h reads
     kv head h // (heads / kv_heads) (src/kernels.rs:1166); keys up to the query's
     own position, or the last ``window`` of them; o projection.
+
+    Further terms, each absent by default: ``softcap`` c replaces a score s by
+    c * tanh(s / c) (after the scaling); ``sinks`` gives every query head a learned
+    logit (tensor ``sink`` [heads]) that stands in the softmax's denominator as
+    exp(sink) beside the keys' terms and has no value; ``values_are_keys`` takes
+    the values to be the keys as projected, before the rotation (there is no v
+    projection; the cache still holds both, the keys rotated).  ``names`` replaces
+    local tensor names (keys: q, k, v, o, q_norm, k_norm, sink).
     """
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
+             "o": "o_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+             "sink": "sink"}
 
     def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, n_kv_heads: int,
                  head_dim: int, position: PartSpec, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None, scale: Optional[float] = None,
-                 shares_kv: bool = False):
+                 shares_kv: bool = False, softcap: Optional[float] = None, sinks: bool = False,
+                 values_are_keys: bool = False, names: Optional[dict] = None):
         super().__init__(ctx)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
@@ -67,6 +80,13 @@ class GQAAttention(Mixer):
         # queries only, stores nothing and owns no cache (the schedule says whose
         # cache it is given)
         self.shares_kv = bool(shares_kv)
+        self.softcap = float(softcap) if softcap else None
+        self.has_sinks, self.values_are_keys = bool(sinks), bool(values_are_keys)
+        if self.values_are_keys and (self.shares_kv or qk_norm_eps is not None):
+            raise ValueError("values that are the keys go with a cache of the layer's own and "
+                             "with keys that are not normalised")
+        self.names = dict(self.NAMES, **(names or {}))
+        self.sink = None
         self.position = build_part("position", position, ctx)
         self.qkv = self.o = None
         self.q_norm_w = self.k_norm_w = None
@@ -75,29 +95,35 @@ class GQAAttention(Mixer):
         return (self.position,)
 
     def param_specs(self):
-        H, nq, nkv, D = self.hidden, self.nq, self.nkv, self.D
-        specs = {"q_proj.weight": ParamSpec((nq * D, H)), "o_proj.weight": ParamSpec((H, nq * D))}
+        H, nq, nkv, D, nm = self.hidden, self.nq, self.nkv, self.D, self.names
+        specs = {nm["q"]: ParamSpec((nq * D, H)), nm["o"]: ParamSpec((H, nq * D))}
         if not self.shares_kv:
-            specs["k_proj.weight"] = ParamSpec((nkv * D, H))
-            specs["v_proj.weight"] = ParamSpec((nkv * D, H))
+            specs[nm["k"]] = ParamSpec((nkv * D, H))
+            if not self.values_are_keys:
+                specs[nm["v"]] = ParamSpec((nkv * D, H))
         if self.qk_norm_eps is not None:
-            specs["q_norm.weight"] = ParamSpec((D,), "vector")
+            specs[nm["q_norm"]] = ParamSpec((D,), "vector")
             if not self.shares_kv:
-                specs["k_norm.weight"] = ParamSpec((D,), "vector")
+                specs[nm["k_norm"]] = ParamSpec((D,), "vector")
+        if self.has_sinks:
+            specs[nm["sink"]] = ParamSpec((nq,), "offset")
         return specs
 
     def load(self, params):
-        ws = [params["q_proj.weight"]]
+        nm = self.names
+        ws = [params[nm["q"]]]
         if not self.shares_kv:
-            ws += [params["k_proj.weight"], params["v_proj.weight"]]
+            ws += [params[nm["k"]]] + ([] if self.values_are_keys else [params[nm["v"]]])
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must be stored in one dtype to be fused")
         self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
-        self.o = Linear(params["o_proj.weight"], self.ctx.products)
+        self.o = Linear(params[nm["o"]], self.ctx.products)
         if self.qk_norm_eps is not None:
-            self.q_norm_w = params["q_norm.weight"].contiguous()
+            self.q_norm_w = params[nm["q_norm"]].contiguous()
             if not self.shares_kv:
-                self.k_norm_w = params["k_norm.weight"].contiguous()
+                self.k_norm_w = params[nm["k_norm"]].contiguous()
+        if self.has_sinks:       # 32-bit, as the scores are
+            self.sink = params[nm["sink"]].float().contiguous()
 
     def kernel_modules(self):
         mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules() + self.o.kernel_modules()
@@ -131,10 +157,11 @@ class GQAAttention(Mixer):
             if rot is None:
                 q, _k = self.position.apply_qk(q, q[:, :0], step.token_pos)
             attn = ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
-                                 step=step, page=cache.page, scale=self.scale, window=self.window)
+                                 step=step, page=cache.page, scale=self.scale, window=self.window,
+                                 softcap=self.softcap, sinks=self.sink)
             return self.o(attn.view(T, self.nq * self.D), partial_ok=True)
         common = dict(q_w=self.q_norm_w, k_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
-                      token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)
+                      values_are_keys=self.values_are_keys, token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)
         if fused:
             q, _ = ops.qk_prepare(qkv, self.nq, self.nkv, self.D,
                                   inv_freq=rot.inv_freq if rot else None,
@@ -153,5 +180,6 @@ class GQAAttention(Mixer):
                          v_pages=cache.v_pages, page=cache.page)
             q = q.contiguous()
         attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
-                             page=cache.page, scale=self.scale, window=self.window)
+                             page=cache.page, scale=self.scale, window=self.window,
+                             softcap=self.softcap, sinks=self.sink)
         return self.o(attn.view(T, self.nq * self.D), partial_ok=True)

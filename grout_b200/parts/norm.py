@@ -7,7 +7,12 @@
   stream with its normalised rows.  ``delta`` may also arrive as a stack of
   32-bit partial sums [S, T, N] (a split-K projection leaves its reduction to
   the norm); they are added in order.  The default does the steps one after the
-  other; RMSNorm does all of it in one kernel.
+  other; RMSNorm does all of it in one kernel.  ``delta`` may, thirdly, be a
+  ``Contribution``: a sublayer's output that passes through a norm of its own and
+  a constant factor on its way into the stream ("sandwich" layers), with, if the
+  model has one, a vector that is added to every row on the same occasion.
+  ``LayerNorm`` does all of that in its one kernel as well; every other norm
+  resolves the contribution first and goes on as above.
 """
 from __future__ import annotations
 
@@ -15,8 +20,47 @@ from typing import Optional, Tuple
 
 import torch
 
+from dataclasses import dataclass
+
 from ..kernels import ops
 from .base import BuildContext, ParamSpec, Part, register_part
+
+
+@dataclass
+class Contribution:
+    """What is about to be added to the residual stream: ``mult * norm(delta)``
+    (just ``delta`` without a norm; nothing when ``delta`` is None) plus
+    ``offset`` on every row.  ``delta`` is [T, N] in the compute dtype or a stack of
+    32-bit partial sums [S, T, N]; ``offset`` a 32-bit vector [N]."""
+    delta: Optional[torch.Tensor]
+    norm: Optional["Norm"] = None
+    mult: float = 1.0
+    offset: Optional[torch.Tensor] = None
+
+    def resolved(self) -> Optional[torch.Tensor]:
+        """The contribution as one 32-bit tensor [T, N] (step by step, for norms
+        without a kernel that takes it whole); None when there is nothing."""
+        d = self.delta
+        if d is not None and d.dim() == 3:
+            d = d.sum(dim=0)
+        if d is not None and self.norm is not None:
+            d = self.norm.forward(d if d.dtype == self.norm.ctx.dtype
+                                  else ops.cast(d, self.norm.ctx.dtype))
+        if d is not None:
+            d = d.float() * self.mult if self.mult != 1.0 else d.float()
+        if self.offset is not None:
+            d = self.offset.float()[None, :] if d is None else d + self.offset.float()[None, :]
+        return d
+
+
+def with_offset(pending, offset: torch.Tensor) -> Contribution:
+    """``pending`` (a tensor, a ``Contribution`` or None) with ``offset`` added to
+    every row as well."""
+    if isinstance(pending, Contribution):
+        if pending.offset is not None:
+            offset = pending.offset + offset
+        return Contribution(pending.delta, pending.norm, pending.mult, offset)
+    return Contribution(pending, None, 1.0, offset)
 
 
 class Norm(Part):
@@ -27,6 +71,8 @@ class Norm(Part):
 
     def add_norm(self, res: Optional[torch.Tensor], delta: Optional[torch.Tensor],
                  rows: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        if isinstance(delta, Contribution):
+            delta = delta.resolved()
         res = residual_add(res, delta, rows)
         return res, self.forward(ops.cast(res, self.ctx.dtype))
 
@@ -37,6 +83,8 @@ def residual_add(res, delta, rows=None) -> torch.Tensor:
     if delta is not None and delta.dim() == 3:      # partial sums of a split-K product
         delta = delta.sum(dim=0)
     if res is None:
+        if delta is None:
+            raise ValueError("neither a residual stream nor a contribution to it")
         out = delta.float()
     elif delta is None:
         out = res
@@ -73,4 +121,64 @@ class RMSNorm(Norm):
         return y
 
     def add_norm(self, res, delta, rows=None):
+        if isinstance(delta, Contribution):      # resolved step by step, added in 32-bit
+            res, delta = residual_add(res, delta.resolved()), None
         return ops.add_rmsnorm(res, delta, self.weight, self.eps, dtype=self.ctx.dtype, rows=rows)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b over the last axis, var the mean
+    of the squared deviations; mean, variance and the scaling are 32-bit.  The
+    bias may be absent (``bias=False``), and with ``center=False`` the mean is not
+    taken off (x / sqrt(mean(x^2) + eps) * w + b).  ``weight_name`` and
+    ``bias_name`` are the tensors' local names."""
+
+    def __init__(self, ctx: BuildContext, dim: int, eps: float, bias: bool = True,
+                 center: bool = True, weight_name: str = "weight", bias_name: str = "bias"):
+        super().__init__(ctx)
+        self.dim, self.eps = int(dim), float(eps)
+        self.has_bias, self.center = bool(bias), bool(center)
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.weight = self.bias = None
+
+    def param_specs(self):
+        specs = {self.weight_name: ParamSpec((self.dim,), "vector")}
+        if self.has_bias:
+            specs[self.bias_name] = ParamSpec((self.dim,), "offset")
+        return specs
+
+    def load(self, params):
+        # 32-bit whatever the checkpoint stores: the norm's arithmetic is 32-bit
+        self.weight = params[self.weight_name].float().contiguous()
+        self.bias = params[self.bias_name].float().contiguous() if self.has_bias else None
+
+    def kernel_modules(self):
+        return ("layernorm",)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x):
+        _res, y = ops.add_layernorm(None, x, self.weight, self.bias, self.eps, self.center,
+                                    dtype=self.ctx.dtype, write_res=False)
+        return y
+
+    def add_norm(self, res, delta, rows=None):
+        post = None
+        mult, offset = 1.0, None
+        if isinstance(delta, Contribution):
+            c, delta = delta, delta.delta
+            mult, offset = c.mult, c.offset
+            if c.norm is not None and delta is not None:
+                if not isinstance(c.norm, LayerNorm):
+                    delta, mult = Contribution(delta, c.norm, mult).resolved(), 1.0
+                    res, delta = residual_add(res, delta), None
+                else:
+                    post = c.norm
+        return ops.add_layernorm(res, delta, self.weight, self.bias, self.eps, self.center,
+                                 dtype=self.ctx.dtype, rows=rows, mult=mult, offset=offset,
+                                 post_weight=post.weight if post else None,
+                                 post_bias=post.bias if post else None,
+                                 post_eps=post.eps if post else 0.0,
+                                 post_center=post.center if post else True)

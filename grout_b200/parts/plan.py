@@ -11,7 +11,10 @@ needs them, new parts.
   ``ScheduleEntry(layer, cache_of)``.  A layer may be named twice (its weights
   run twice; each run that owns a cache has its own), and an entry may read
   another entry's cache instead of owning one (``cache_of`` = index into the
-  schedule).
+  schedule).  ``add`` = (name, row) adds row ``row`` of the model-level tensor
+  ``name`` (declared in ``ModelPlan.stream_vectors``) to every row of the
+  residual stream right before the entry's layer runs: what a model that goes
+  through a run of layers several times adds in front of each pass.
 """
 from __future__ import annotations
 
@@ -32,6 +35,7 @@ class LayerPlan:
 class ScheduleEntry:
     layer: int
     cache_of: Optional[int] = None        # schedule index whose cache this entry uses
+    add: Optional[Tuple[str, int]] = None # (stream vector's tensor name, row) added before it runs
 
 
 @dataclass(frozen=True)
@@ -47,10 +51,18 @@ class ModelPlan:
     vocab_size: int
     max_position: int                     # longest sequence the architecture allows
     stop_tokens: Tuple[int, ...] = ()
+    stream_vectors: Tuple[Tuple[str, Tuple[int, int]], ...] = ()   # (tensor name, [rows, hidden])
+    # tensors that a checkpoint may hold although nothing reads them (name, shape)
+    unread_tensors: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
     def validate(self) -> None:
         n = len(self.layers)
+        vectors = dict(self.stream_vectors)
         for i, e in enumerate(self.schedule):
+            if e.add is not None and (e.add[0] not in vectors or
+                                      not 0 <= e.add[1] < vectors[e.add[0]][0]):
+                raise ValueError(f"schedule entry {i} adds row {e.add[1]} of '{e.add[0]}', which "
+                                 f"the plan does not declare")
             if not 0 <= e.layer < n:
                 raise ValueError(f"schedule entry {i} names layer {e.layer} of {n}")
             if e.cache_of is not None:

@@ -3,8 +3,9 @@
 ``write_random_model(config_dict, seed, folder)`` writes a model folder
 (config.json, model.safetensors) that every loader of this format can read;
 ``random_tensors`` yields the same tensors without a file, for models too large
-to be worth writing.  Every matrix and embedding is N(0, 0.02^2) and every
-vector (norm weights) 1 + N(0, 0.1^2).  Each tensor has its own generator,
+to be worth writing.  Every matrix and embedding is N(0, 0.02^2), every
+vector (norm weights) 1 + N(0, 0.1^2) and every offset (biases, vectors that are
+added to something) N(0, 0.1^2).  Each tensor has its own generator,
 seeded from (seed, tensor name), so a tensor's values do not depend on which
 other tensors are made or in which order.
 
@@ -42,6 +43,8 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, dtype=torch.bfloat16,
     x = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
     if spec.kind == "vector":
         x = 1.0 + VECTOR_STD * x
+    elif spec.kind == "offset":
+        x = VECTOR_STD * x
     else:
         x = MATRIX_STD * x
     return x.to(dtype)
