@@ -37,6 +37,8 @@ struct DecodeArgs {
   float* part_ml;          // [n_seqs, nq, n_splits, 2]
   int n_seqs, nq, nkv, max_pages, page, window, n_splits;
   float scale_log2;
+  const float* sinks;      // [nq] one more logit of every head's denominator, or null
+  ScoreCap cap;            // the score cap (off when cap_log2 == 0)
 };
 
 template <int DT>
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     }
     WarpAttn<DT> w;
     w.init();
+    w.cap = a.cap;
     int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
 #pragma unroll
     for (int s = 0; s < DC_STAGES; ++s) {   // what had to wait for the producer
@@ -212,6 +215,8 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
         O += red_o[((size_t)wi * 16 + row) * D + d] * f;
       }
       if (single) {
+        // the sink joins the finished row; with splits the second kernel adds it, once
+        if (a.sinks) O *= add_sink(a.sinks[h0 + row], M, L);
         a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(O / L);
       } else {
         const size_t p = ((size_t)seq * a.nq + h0 + row) * a.n_splits + split;
@@ -239,7 +244,8 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
 // A separate, wide launch: the combination is a few hundred independent loads
 // per output row, which one block per kv head would have to do alone.
 __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_ml,
-                                         bf16* __restrict__ out, int n_splits, int D) {
+                                         bf16* __restrict__ out, int n_splits, int D,
+                                         const float* __restrict__ sinks, int nq) {
   pdl_launch_dependents_if_small();
   pdl_wait();
   // Loads are requested eight splits at a time and then used in split order: a loop that
@@ -256,8 +262,11 @@ __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_
     for (int u = 0; u < 8; ++u) M = fmaxf(M, v[u].x);
   }
   pdl_launch_dependents_if_large();
+  // the sink is a split of its own with sum 1 and no accumulator
+  const float sk = sinks ? sinks[blockIdx.x % nq] * 1.4426950408889634f : -INFINITY;
+  M = fmaxf(M, sk);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float L = 0.f, O = 0.f;
+    float L = sinks ? exp2f(sk - M) : 0.f, O = 0.f;
     for (int s0 = 0; s0 < n_splits; s0 += 8) {
       float2 v[8];
       float o[8];
@@ -297,7 +306,8 @@ static int launch(const DecodeArgs& a, cudaStream_t s) {
                     smem, s, a);
   if (e || a.n_splits == 1) return e;
   return gb_launch(attn_decode_merge_kernel, dim3(a.n_seqs * a.nq), dim3(D < 128 ? D : 128), 0, s,
-                   (const float*)a.part_o, (const float*)a.part_ml, a.out, a.n_splits, D);
+                   (const float*)a.part_o, (const float*)a.part_ml, a.out, a.n_splits, D, a.sinks,
+                   a.nq);
 }
 
 // Refuses (GB_ERR_UNSUPPORTED) head sizes that are no multiple of 16 or above

@@ -50,6 +50,8 @@ struct DecodeTmaArgs {
   int n_seqs, nq, nkv, max_pages, window, n_splits;
   float scale_log2;
   unsigned long long* stamps;   // optional [blocks][12] %globaltimer stamps of a block's phases (tuning), or null
+  const float* sinks;      // [nq] one more logit of every head's denominator, or null
+  ScoreCap cap;            // the score cap (off when cap_log2 == 0)
 };
 
 #define DA_STAMP(slot)                                                                          \
@@ -164,6 +166,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   if (tid == 0) DA_STAMP(3);
   WarpAttn<DT> w;
   w.init();
+  w.cap = a.cap;
   if (my_tiles > 0) {
     // the query tile: G rows, the rest zero
     const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
@@ -276,6 +279,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         O += red_o[((size_t)wi * 16 + row) * (D + 8) + d] * f;
       }
       if (single) {
+        // the sink joins the finished row; with splits the combining block adds it, once
+        if (a.sinks) O *= add_sink(a.sinks[h0 + row], M, L);
         a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(O / L);
       } else {
         const size_t p = ((size_t)seq * a.nq + h0 + row) * a.n_splits + split;
@@ -358,7 +363,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
       for (int u = 0; u < 8; ++u) M = fmaxf(M, m2[u].x);
     }
-    float L = 0.f, O[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // the sink is a split of its own with sum 1 and no accumulator
+    const float sk = a.sinks ? a.sinks[h0 + row] * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sk);
+    float L = a.sinks ? exp2f(sk - M) : 0.f, O[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s0 = 0; s0 < S; s0 += 8) {
       if (s0) request(s0);
 #pragma unroll

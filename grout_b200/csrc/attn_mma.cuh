@@ -11,6 +11,13 @@
 // scale * log2(e), as the reference's fmha kernels do (src/kernels.rs:1195-1291).
 // Probabilities are rounded to bf16 for the P.V product (the reference rounds
 // them to f16, src/kernels.rs:1282) while l sums the unrounded values.
+//
+// Two further terms, off unless asked for.  A score cap C replaces s * scale by
+// C * tanh(s * scale / C) before the log2 domain is entered (ScoreCap; the tanh
+// is 1 - 2 / (2^(2x log2 e) + 1), two special-function instructions, accurate to
+// the unit's 2^-22 or so of absolute error).  A sink is one more term 2^(sink
+// log2 e - m) of a row's denominator, without a value: add_sink() folds it into a
+// finished (m, l) and returns the factor that the row's accumulator takes.
 #pragma once
 #include "common.cuh"
 
@@ -47,6 +54,36 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// log2_e * C and scale / C of a score cap C; cap_log2 == 0 means no cap.
+struct ScoreCap {
+  float cap_log2, cap_inv;
+};
+static inline ScoreCap make_score_cap(float softcap, float scale) {
+  ScoreCap c;
+  c.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  c.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+  return c;
+}
+// tanh(x) = 1 - 2 / (e^(2x) + 1); exact at both ends (e^(2x) = inf gives 1, 0 gives -1).
+__device__ __forceinline__ float tanh_by_exp(float x) {
+  const float e = exp2f(x * 2.8853900817779268f);
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+// A score already multiplied by scale / C -> its capped value in the log2 domain.
+__device__ __forceinline__ float capped_log2(float x, const ScoreCap& c) {
+  return c.cap_log2 * tanh_by_exp(x);
+}
+// Folds the sink (natural-log units) into a row's finished maximum m (log2 domain)
+// and sum l; returns the factor by which the row's accumulator must be multiplied.
+__device__ __forceinline__ float add_sink(float sink, float& m, float& l) {
+  const float sk = sink * 1.4426950408889634f;
+  const float m_new = fmaxf(m, sk);
+  const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+  l = l * f + exp2f(sk - m_new);
+  m = m_new;
+  return f;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -78,8 +115,10 @@ struct WarpAttn {
   uint32_t q[DT][4];                // A fragments of the 16 x D query tile
   float o[2 * DT][4];               // 16 x D accumulator
   float m[2], l[2];                 // running max (already times c) and this lane's share of l
+  ScoreCap cap;                     // the score cap, off after init()
 
   __device__ __forceinline__ void init() {
+    cap.cap_log2 = cap.cap_inv = 0.f;
 #pragma unroll
     for (int i = 0; i < 2 * DT; ++i)
 #pragma unroll
@@ -138,6 +177,13 @@ struct WarpAttn {
     between();
     // scale into the log2 domain, mask, row maxima
     float mx[2] = {-INFINITY, -INFINITY};
+    if (cap.cap_log2 != 0.f) {   // the same for every thread of the kernel
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = capped_log2(s[j][e] * cap.cap_inv, cap);
+      c = 1.f;
+    }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
 #pragma unroll

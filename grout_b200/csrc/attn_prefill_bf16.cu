@@ -28,6 +28,8 @@ struct PrefillArgs {
   bf16* out;               // [n_tokens, nq, D]
   int n_seqs, nq, nkv, max_pages, window, n_qblocks;
   float scale_log2;        // scale * log2(e)
+  const float* sinks;      // [nq] one more logit of every head's denominator, or null
+  ScoreCap cap;            // the score cap (off when cap_log2 == 0)
 };
 
 template <int DT>
@@ -102,6 +104,7 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
 
   WarpAttn<DT> w;
   w.init();
+  w.cap = a.cap;
   // rows of this lane: warp * 16 + g and + 8
   int lo[2], hi[2];
 #pragma unroll
@@ -140,7 +143,8 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PrefillA
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + g + r * 8;
     if (row >= rows) continue;
-    const float inv = 1.0f / w.l[r];
+    const float f = a.sinks ? add_sink(a.sinks[h], w.m[r], w.l[r]) : 1.f;
+    const float inv = f / w.l[r];
     bf16* orow = out + (size_t)row * tok_stride;
 #pragma unroll
     for (int i = 0; i < 2 * DT; ++i) {

@@ -53,6 +53,7 @@
 // its SM: this is how the order in which blocks reach the SMs was seen.
 // Tuning aids; never defined in the product build.
 #include "tc_common.cuh"
+#include "attn_mma.cuh"   // ScoreCap, add_sink
 
 #define AT_BM 128
 #define AT_BN 64
@@ -68,6 +69,8 @@ struct AttnTcArgs {
   int* error;
   int n_seqs, nq, nkv, max_pages, window, n_qblocks;
   float scale_log2;
+  const float* sinks;      // [nq] one more logit of every head's denominator, or null
+  ScoreCap cap;            // the score cap (off when cap_log2 == 0)
 };
 
 // V tile as the B operand of R = P V: N (head_dim) is the contiguous direction
@@ -449,6 +452,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int j_mask = (a.window > 0 || rows_mine < AT_BM) ? 0 : max(0, (pos0 + g * AT_BM + 1) / AT_BN - tile_lo);
     const uint32_t p_row = smem_u32(p_s + (g * 2) * Cfg::P_BYTES + r * 128), p_swz = (uint32_t)(r & 7) << 4;
     float m_used = -INFINITY, l = 0.f;             // base of the exponent (scaled), row sum
+    const bool capped = a.cap.cap_log2 != 0.f;     // capped scores are in the log2 domain already
+    const float score_scale = capped ? 1.0f : a.scale_log2;
     bool ok = true;
 #ifdef AT_STAMPS
     const bool stamping = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && q == 1;
@@ -502,6 +507,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         __syncwarp();
         mbar_arrive_if(&s_empty[g], lane == 0);   // S is in registers: the next S may be written
         AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 2)
+        if (capped) {   // scores enter the log2 domain here, through the cap
+#pragma unroll
+          for (int c = 0; c < AT_BN; ++c) s[c] = capped_log2(s[c] * a.cap.cap_inv, a.cap);
+        }
         if (need_mask) {
           const int last = hi - key0, first = lo - key0;   // this row's keys of the tile
           if (a.window > 0) {
@@ -524,7 +533,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
           mx4[3] = max3(mx4[3], s[c + 6], s[c + 7]);
         }
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * score_scale;
       }
 
       // raise the base only when the maximum outgrew it by 2^8 (or on the first keys)
@@ -560,7 +569,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const float mbase = (m_used == -INFINITY) ? 0.f : m_used;
       uint64_t sum4[4];                                  // four pairs of partial sums
       uint32_t pk[AT_BN / 2];
-      const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), base2 = pack_f32x2(-mbase, -mbase);
+      const uint64_t scale2 = pack_f32x2(score_scale, score_scale), base2 = pack_f32x2(-mbase, -mbase);
 #pragma unroll
       for (int c = 0; c < AT_BN; c += 2) {
         float x0, x1;
@@ -604,7 +613,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
     } else if (n_mine > 0) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      const float sink_f = a.sinks ? add_sink(a.sinks[h], m_used, l) : 1.0f;
+      const float inv = sink_f / l;
       bf16* orow = a.out + ((size_t)(tok0 + g * AT_BM + r) * a.nq + h) * D;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {

@@ -91,7 +91,8 @@ struct TcArgs {
   int* error;           // device int, 0 while all is well
   int rowsA, rowsB, K, ld;
   int transpose_out, out_f32;
-  int silu;             // transposed output only: rows of A are gate|up interleaved in eights
+  int silu;             // 1 (transposed output only): rows of A are gate|up interleaved in eights;
+                        // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
   unsigned long long* stamps;   // optional [blocks][8] %globaltimer stamps of the phases, or null
   int split_k;          // > 0: plain split-K, see below
@@ -468,7 +469,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // put together in shared memory instead and written as whole 128-byte rows.  (At the
       // 4B sizes and batch 64 the epilogue of the one tile a block has is not hidden behind
       // anything: 3.6 of the product's 22 us.)
-      const bool staged = Cfg::EPI_BYTES > 0 && a.transpose_out && a.silu && !a.out_f32 && (a.ld & 7) == 0 &&
+      const bool staged = Cfg::EPI_BYTES > 0 && a.transpose_out && a.silu == 1 && !a.out_f32 && (a.ld & 7) == 0 &&
                           (((uintptr_t)a.out) & 15) == 0;
       if (write_out) {
 #pragma unroll 1
@@ -511,8 +512,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             }
           }
+          if (a.silu == 2) {   // the finished sums, squared in 32-bit before the one rounding
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float p = fmaxf(f[j], 0.f);
+              f[j] = p * p;
+            }
+          }
           // store 16 columns of row r
-          if (a.transpose_out && a.silu) {
+          if (a.transpose_out && a.silu == 1) {
             // rows 16t..16t+7 of A are gates and 16t+8..16t+15 the matching ups: the up
             // of this lane's gate sits 8 lanes further; out[col_b][feature] = silu(g) * u
             // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296, as an epilogue)
@@ -873,7 +881,8 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   if (e) return e;
   if (!A || !B || !args->out || !args->scratch || !args->counters || !args->error) return GB_ERR_BAD_ARG;
   if ((((uintptr_t)A) | ((uintptr_t)B)) & 15) return GB_ERR_BAD_ARG;
-  if (args->silu && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
+  if (args->silu == 1 && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
+  if (args->silu < 0 || args->silu > 2) return GB_ERR_BAD_ARG;
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;

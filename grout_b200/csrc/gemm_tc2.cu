@@ -47,7 +47,8 @@ struct Tc2Args {
   int* error;    // device int, 0 while all is well
   int M, N, K, ld;
   int out_f32;
-  int silu;      // columns of W^T are gate|up interleaved in eights; out is [M, N / 2]
+  int silu;      // 1: columns of W^T are gate|up interleaved in eights; out is [M, N / 2]
+                 // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int bn;        // columns of C per tile: a multiple of 16, 32..256 (filled in by the launcher)
 };
 
@@ -226,7 +227,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // ------------------------------------------------------------------ epilogue (both blocks)
     const int q = warp & 3;   // the TMEM lanes this warp may touch
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int n_out = a.silu ? a.N / 2 : a.N;
+    const int n_out = a.silu == 1 ? a.N / 2 : a.N;
     int t = 0;
     bool ok = true;
     for (int tile = cluster; tile < n_tiles && ok; tile += n_clusters, ++t) {
@@ -249,7 +250,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         tc_wait_ld();
         const int col = col0 + c0;
         if (row >= a.M || col >= a.N) continue;
-        if (a.silu) {
+        if (a.silu == 2) {   // squared in 32-bit before the one rounding
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float p = fmaxf(__uint_as_float(v[c]), 0.f);
+            v[c] = __float_as_uint(p * p);
+          }
+        }
+        if (a.silu == 1) {
           uint32_t w[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -321,7 +329,8 @@ GB_EXPORT int gb_gemm_tc2_bf16(const void* X, const void* W, const Tc2Args* args
   if (!X || !W || !a.out || !a.error || a.M <= 0 || a.N <= 0 || a.K <= 0) return GB_ERR_BAD_ARG;
   if (a.K % 8) return GB_ERR_UNSUPPORTED;
   if ((((uintptr_t)X) | ((uintptr_t)W) | ((uintptr_t)a.out)) & 15) return GB_ERR_BAD_ARG;
-  if (a.silu && (a.N % 16 || a.out_f32)) return GB_ERR_UNSUPPORTED;
+  if (a.silu == 1 && (a.N % 16 || a.out_f32)) return GB_ERR_UNSUPPORTED;
+  if (a.silu < 0 || a.silu > 2) return GB_ERR_BAD_ARG;
   if ((a.ld * (a.out_f32 ? 4 : 2)) % 16) return GB_ERR_UNSUPPORTED;
   static int sms = 0;
   static bool configured = false;

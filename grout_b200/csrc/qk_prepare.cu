@@ -399,6 +399,162 @@ __global__ void __launch_bounds__(128, 8) qk_prepare_wide_kernel(const QkPrepare
   pdl_launch_dependents();
 }
 
+
+// Heads whose rotation covers only their first rot_dim elements, or whose values
+// are their keys before the rotation (bf16 activations).  A lane takes eight
+// consecutive elements of a head (one 16-byte piece, or two pieces of each 32-bit
+// partial sum), so a head is D / 8 lanes and a warp prepares 32 / (D / 8) heads at a
+// time; element i < rot_dim / 2 turns together with element i + rot_dim / 2, which
+// lies (rot_dim / 16) lanes further on in the same warp and comes by shuffle.  The
+// token's sines and cosines are computed once per block and shared.  D / 8 is a
+// power of two up to 32 and rot_dim / 2 a multiple of 8.
+template <typename WT>
+__global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareArgs a) {
+  extern __shared__ float sc_s[];                // [rot_dim / 2] sines, then as many cosines
+  const int D = a.D, LPH = D >> 3, HPW = 32 / LPH, half = a.rot_dim >> 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int sub = lane / LPH, ci = lane % LPH, j0 = ci * 8;
+  const int t = blockIdx.x;
+  const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
+  pdl_launch_dependents_if_small();
+  // what no kernel of this step writes comes before the wait for the projection
+  const int pos = a.token_pos[t];
+  if (a.inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x)
+      sincosf((float)pos * a.inv_freq[j], &sc_s[j], &sc_s[half + j]);
+  }
+  size_t page_row0 = 0;   // row of (page of pos, kv head 0, pos in page)
+  bool paged = false;
+  if (a.k_pages) {
+    const int slot = a.slots[a.token_seq[t]];
+    if (slot >= 0) {
+      page_row0 = paged_row(a.block_table + (size_t)slot * a.max_pages, pos, 0, a.nkv, a.page, D);
+      paged = true;
+    }
+  }
+  __syncthreads();
+  // this lane's part in the rotation: none, the first of a pair, or the second
+  const int role = (!a.inv_freq || j0 >= a.rot_dim) ? 0 : (j0 < half ? 1 : 2);
+  const int partner = role == 1 ? lane + (half >> 3) : (role == 2 ? lane - (half >> 3) : lane);
+  float sn[8], cs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    sn[e] = role ? sc_s[(j0 + e) % half] : 0.f;
+    cs[e] = role ? sc_s[half + (j0 + e) % half] : 1.f;
+    if (role == 1) sn[e] = -sn[e];               // x cos - partner sin; the second: x cos + partner sin
+  }
+  pdl_wait();
+  const int passes = (n_heads + HPW - 1) / HPW;
+  for (int pass = blockIdx.y * warps + warp; pass < passes; pass += gridDim.y * warps) {
+    const int head = pass * HPW + sub;
+    const bool live = head < n_heads;            // every lane walks the loop: shuffles are warp-wide
+    const size_t at = ((size_t)t * n_heads + (live ? head : 0)) * D + j0;
+    float x[8];
+    if (a.qkv_parts) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = 0.f;
+      for (int k0 = 0; k0 < a.n_parts; k0 += 4) {   // four partials requested at once, added in order
+        float4 pa[4], pb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int k = k0 + u < a.n_parts ? k0 + u : a.n_parts - 1;
+          const float4* ps = reinterpret_cast<const float4*>(a.qkv_parts + (size_t)k * a.part_stride + at);
+          pa[u] = ps[0], pb[u] = ps[1];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (k0 + u < a.n_parts) {
+            x[0] += pa[u].x, x[1] += pa[u].y, x[2] += pa[u].z, x[3] += pa[u].w;
+            x[4] += pb[u].x, x[5] += pb[u].y, x[6] += pb[u].z, x[7] += pb[u].w;
+          }
+      }
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>((const bf16*)a.qkv + at);
+      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&rw[i]);
+        x[2 * i] = __low2float(v2), x[2 * i + 1] = __high2float(v2);
+      }
+    }
+    const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+    const WT* wn = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
+    {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+      for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (wn) {
+        const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * to_f32<WT>(wn[j0 + e]);
+      }
+    }
+    auto pack8 = [](const float (&v)[8]) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&p2);
+      }
+      return make_uint4(w[0], w[1], w[2], w[3]);
+    };
+    const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
+    if (a.v_from_k && kind == 1 && live) {        // the value: the key as it stands before it turns
+      const uint4 v8 = pack8(x);
+      if (a.kv_out)
+        *reinterpret_cast<uint4*>((bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + a.nkv + hh) * D + j0) = v8;
+      if (paged)
+        *reinterpret_cast<uint4*>((bf16*)a.v_pages + page_row0 + (size_t)hh * a.page * D + j0) = v8;
+    }
+    if (a.inv_freq) {                             // the same for the whole warp: shuffles inside
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_sync(0xffffffffu, x[e], partner);
+        y[e] = x[e] * cs[e] + other * sn[e];
+      }
+      if (kind != 2) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = y[e];
+      }
+    }
+    if (!live) continue;
+    const uint4 o8 = pack8(x);
+    if (kind == 0) {
+      *reinterpret_cast<uint4*>((bf16*)a.q_out + ((size_t)t * a.nq + head) * D + j0) = o8;
+    } else {
+      if (a.kv_out)
+        *reinterpret_cast<uint4*>((bf16*)a.kv_out +
+                                  ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D + j0) = o8;
+      if (paged)
+        *reinterpret_cast<uint4*>((bf16*)(kind == 1 ? a.k_pages : a.v_pages) + page_row0 +
+                                  (size_t)hh * a.page * D + j0) = o8;
+    }
+  }
+  pdl_launch_dependents_if_large();
+}
+
+static bool chunk_ok(const QkPrepareArgs& a) {
+  auto al = [](const void* p) { return (((uintptr_t)p) & 15) == 0; };
+  const int lph = a.D / 8;
+  return a.D % 8 == 0 && lph <= 32 && (lph & (lph - 1)) == 0 &&
+         (!a.inv_freq || ((a.rot_dim / 2) % 8 == 0 && a.rot_dim <= 1024)) && al(a.qkv) && al(a.q_out) &&
+         al(a.kv_out) && al(a.k_pages) && al(a.v_pages) && al(a.qkv_parts) && (a.part_stride & 3) == 0;
+}
+
+template <typename WT>
+static int launch_chunk(const QkPrepareArgs& a, cudaStream_t stream) {
+  const int warps = 4;
+  const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
+  const int hpw = 32 / (a.D / 8);
+  const int passes = (n_heads + hpw - 1) / hpw;
+  // few tokens: a warp per pass; many: a block walks all of a token's heads
+  const int gy = a.n_tokens >= 128 ? 1 : (passes + warps - 1) / warps;
+  const size_t smem = a.inv_freq ? (size_t)a.rot_dim * sizeof(float) : 0;
+  return gb_launch(qk_prepare_chunk_kernel<WT>, dim3(a.n_tokens, gy), dim3(warps * 32), smem, stream, a);
+}
+
 template <typename WT>
 static int launch_wide(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
@@ -477,6 +633,7 @@ GB_EXPORT int gb_qk_prepare_bf16(const QkPrepareArgs* a, int w_is_f32, cudaStrea
   if (a->n_tokens == 0) return 0;
   if (fast_ok(*a) && wide_ok(*a)) return w_is_f32 ? launch_wide<float>(*a, s) : launch_wide<bf16>(*a, s);
   if (fast_ok(*a)) return w_is_f32 ? launch_fast<float>(*a, s) : launch_fast<bf16>(*a, s);
+  if (chunk_ok(*a)) return w_is_f32 ? launch_chunk<float>(*a, s) : launch_chunk<bf16>(*a, s);
   return w_is_f32 ? launch<bf16, float>(*a, s) : launch<bf16, bf16>(*a, s);
 }
 

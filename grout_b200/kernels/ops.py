@@ -719,7 +719,8 @@ def tc_wait_selftest(device, limit_us: int = 1000) -> int:
 @_profiled("gemm_tc_bf16", _cost_gemm)
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                  swap: Optional[bool] = None, silu_mul: bool = False,
-                 stamps: Optional[torch.Tensor] = None, split_out: bool = False) -> torch.Tensor:
+                 stamps: Optional[torch.Tensor] = None, split_out: bool = False,
+                 relu_squared: bool = False) -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
@@ -729,7 +730,8 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     too few tiles to fill the GPU, K is cut S ways and the S 32-bit partial
     products are returned as [S, M, N] for the consumer to add (its norm or q/k
     preparation does so in the kernel it runs anyway); otherwise the result is the
-    ordinary [M, N]."""
+    ordinary [M, N].  ``relu_squared``: every output becomes max(y, 0)^2, squared in
+    32-bit before the rounding (not with ``silu_mul`` or ``split_out``)."""
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -743,6 +745,8 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     swap = (M <= 64) if swap is None else bool(swap)
     if silu_mul and (not swap or N % 16):
         raise KernelError("the interleaved gate|up epilogue needs the swapped layout and N % 16 == 0")
+    if relu_squared and (silu_mul or split_out):
+        raise KernelError("the squared relu goes with neither the gate|up epilogue nor partial sums")
     n_out = N // 2 if silu_mul else N
     y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     if M == 0:
@@ -767,11 +771,13 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
         a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32 or bool(split))
         a.split_k = split
-        a.silu, a.dep_b = int(silu_mul), int(swap)      # the activations are another kernel's output
+        a.silu = 2 if relu_squared else int(silu_mul)
+        a.dep_b = int(swap)                             # the activations are another kernel's output
         a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
             A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16",
-            detail=f" {N}x{K}" + (" silu" if silu_mul else "") + (f" split {split}" if split else ""))
+            detail=f" {N}x{K}" + (" silu" if silu_mul else "") + (" relu2" if relu_squared else "") +
+            (f" split {split}" if split else ""))
     return y
 
 
@@ -811,17 +817,21 @@ def gemm_tc2_pays(M: int, N: int, device, fused_silu: bool) -> bool:
 
 @_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
-                  silu_mul: bool = False, tile_cols: int = 0) -> torch.Tensor:
+                  silu_mul: bool = False, tile_cols: int = 0,
+                  relu_squared: bool = False) -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
     tiles of 256 rows and ``tile_cols`` columns: a multiple of 16 up to 256, by
     default chosen by the kernel's launcher for the shape).  ``silu_mul``: the rows of ``w`` are gate and up rows
-    interleaved in groups of 8 and the result is silu(gate) * up, [M, N / 2]."""
+    interleaved in groups of 8 and the result is silu(gate) * up, [M, N / 2].
+    ``relu_squared`` (instead): every output becomes max(y, 0)^2, squared in 32-bit."""
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"weight is {tuple(w.shape)} for activations of width {K}")
+    if relu_squared and silu_mul:
+        raise KernelError("one epilogue at a time")
     if K % 8:
         raise KernelError(f"gemm_tc2_bf16 needs an inner size that is a multiple of 8, got {K}")
     if out_dtype not in (torch.bfloat16, torch.float32):
@@ -837,7 +847,8 @@ def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     a = _Tc2Args()
     a.out, a.error = y.data_ptr(), _tc_error_flag(x.device).data_ptr()
     a.M, a.N, a.K, a.ld = M, N, K, n_out
-    a.out_f32, a.silu, a.bn = int(out_dtype == torch.float32), int(silu_mul), int(tile_cols)
+    a.out_f32, a.bn = int(out_dtype == torch.float32), int(tile_cols)
+    a.silu = 2 if relu_squared else int(silu_mul)
     with torch.cuda.device(x.device):
         _check(_fn("gemm_tc2", "gb_gemm_tc2_bf16", "pppp")(
             x.data_ptr(), w.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc2_bf16")
@@ -849,14 +860,24 @@ class _PrefillArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("cu_q", _P),
                 ("slots", _P), ("kv_len", _P), ("out", _P), ("n_seqs", _I), ("nq", _I),
                 ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_qblocks", _I),
-                ("scale_log2", _F)]
+                ("scale_log2", _F), ("sinks", _P), ("cap_log2", _F), ("cap_inv", _F)]
 
 
 class _DecodeArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("slots", _P),
                 ("kv_len", _P), ("out", _P), ("part_o", _P), ("part_ml", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("page", _I), ("window", _I),
-                ("n_splits", _I), ("scale_log2", _F)]
+                ("n_splits", _I), ("scale_log2", _F), ("sinks", _P), ("cap_log2", _F),
+                ("cap_inv", _F)]
+
+
+def _set_cap_and_sinks(a, scale: float, softcap: Optional[float], sinks, nq: int) -> None:
+    """Fills the fields that every tensor-core attention kernel's arguments end with: the
+    sinks and the score cap C as (C log2 e, scale / C), zeros for none."""
+    _check_sinks(sinks, nq)
+    a.sinks = _ptr(sinks)
+    a.cap_log2 = float(softcap) * _LOG2E if softcap else 0.0
+    a.cap_inv = float(scale) / float(softcap) if softcap else 0.0
 
 
 _LOG2E = 1.4426950408889634
@@ -906,7 +927,8 @@ def _q_blocks(q_lens, n_qblocks, rows: int, T: int, n_seqs: int) -> int:
 @_profiled("attn_prefill_bf16", _cost_attention)
 def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
                       page: int, scale: float, window: Optional[int] = None,
-                      n_qblocks: Optional[int] = None) -> torch.Tensor:
+                      n_qblocks: Optional[int] = None, softcap: Optional[float] = None,
+                      sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) on the tensor
     cores.  The grid is sized from ``q_lens``, the host's copy of the sequences'
     row counts, or, without them, from ``n_qblocks`` (an upper bound of the
@@ -931,6 +953,7 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
     a.window = int(window or 0)
     a.n_qblocks = _q_blocks(q_lens, n_qblocks, PREFILL_ROWS, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
+    _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_prefill_bf16", "gb_attn_prefill_bf16", "piip")(
         ctypes.addressof(a), D, page, _stream()), "attn_prefill_bf16")
     return out
@@ -939,7 +962,8 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
 class _AttnTcArgs(ctypes.Structure):
     _fields_ = [("block_table", _P), ("cu_q", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
                 ("error", _P), ("n_seqs", _I), ("nq", _I), ("nkv", _I), ("max_pages", _I),
-                ("window", _I), ("n_qblocks", _I), ("scale_log2", _F)]
+                ("window", _I), ("n_qblocks", _I), ("scale_log2", _F), ("sinks", _P),
+                ("cap_log2", _F), ("cap_inv", _F)]
 
 
 PREFILL_TC_ROWS = 0        # query rows per block of the tcgen05 prefill kernel: 128, 256 or 0 = by size
@@ -962,7 +986,9 @@ def attn_prefill_tc_takes(D: int, nq: int, nkv: int, page: int) -> bool:
 @_profiled("attn_prefill_tc", _cost_attention)
 def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
                     page: int, scale: float, window: Optional[int] = None,
-                    rows_per_block: int = 0, n_qblocks: Optional[int] = None) -> torch.Tensor:
+                    rows_per_block: int = 0, n_qblocks: Optional[int] = None,
+                    softcap: Optional[float] = None,
+                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) with both
     products on the tcgen05 tensor cores.  Pages must hold finite values in the
     rows beyond a sequence's length (the cache zero-fills its pages).  The grid is
@@ -991,6 +1017,7 @@ def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_
         prefill_tc_rows(_q_blocks(q_lens, None, 256, T, n_seqs), nq, q.device)
     a.n_qblocks = _q_blocks(q_lens, n_qblocks, rows, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
+    _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_prefill_tc", "gb_attn_prefill_tc", "ppppiliiip")(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), ctypes.addressof(a), T,
         k_pages.shape[0], D, page, rows, _stream()), "attn_prefill_tc")
@@ -1020,7 +1047,8 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
 @_profiled("attn_decode_bf16", _cost_attention)
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
                      max_kv_len: int, window: Optional[int] = None,
-                     n_splits: Optional[int] = None) -> torch.Tensor:
+                     n_splits: Optional[int] = None, softcap: Optional[float] = None,
+                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys (split-K)."""
     _need(q, "q", torch.bfloat16, 3)
     B, nq, D = q.shape
@@ -1048,6 +1076,7 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
     a.part_o, a.part_ml = _ptr(part_o), _ptr(part_ml)
     a.n_seqs, a.nq, a.nkv, a.max_pages, a.page = B, nq, nkv, block_table.shape[1], page
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
+    _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     _check(_fn("attn_decode_bf16", "gb_attn_decode_bf16", "pip")(
         ctypes.addressof(a), D, _stream()), "attn_decode_bf16", 2 if ns > 1 else 1)
     return out
@@ -1057,7 +1086,8 @@ class _DecodeTmaArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("block_table", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
                 ("part_o", _P), ("part_ml", _P), ("counters", _P), ("error", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_splits", _I),
-                ("scale_log2", _F), ("stamps", _P)]
+                ("scale_log2", _F), ("stamps", _P), ("sinks", _P), ("cap_log2", _F),
+                ("cap_inv", _F)]
 
 
 DECODE_TMA_STAMPS: Optional[torch.Tensor] = None      # int64 [blocks, 12] for tuning, or None
@@ -1109,7 +1139,9 @@ def decode_tma_splits(n_seqs: int, nkv: int, max_kv_len: int, device, per_sm: in
 @_profiled("attn_decode_tma", _cost_attention)
 def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
                     max_kv_len: int, window: Optional[int] = None,
-                    n_splits: Optional[int] = None, stages: int = 0) -> torch.Tensor:
+                    n_splits: Optional[int] = None, stages: int = 0,
+                    softcap: Optional[float] = None,
+                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys, the tiles
     brought in by TMA and the splits combined by the block that finishes last (one
     launch).  Heads of 64 or 128, pages of 64 tokens."""
@@ -1144,6 +1176,7 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
     a.n_seqs, a.nq, a.nkv, a.max_pages = B, nq, nkv, block_table.shape[1]
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
     a.stamps = _ptr(DECODE_TMA_STAMPS)
+    _set_cap_and_sinks(a, scale, softcap, sinks, nq)
     with torch.cuda.device(q.device):
         _check(_fn("attn_decode_tma", "gb_attn_decode_tma", "pplpiiip")(
             k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], ctypes.addressof(a), D, page,
@@ -1161,29 +1194,28 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
     ``softcap`` c: scores become c * tanh(score / c); ``sinks`` [nq] float32: one
     more term exp(sinks[h]) in the denominator of query head h."""
     _T, nq, D = q.shape
-    plain_only = bool(softcap) or sinks is not None
-    if q.dtype == torch.bfloat16 and not plain_only and \
-            fast_attention_takes(D, nq, k_pages.shape[1], page):
+    extra = dict(softcap=softcap, sinks=sinks)
+    if q.dtype == torch.bfloat16 and fast_attention_takes(D, nq, k_pages.shape[1], page):
         nkv = k_pages.shape[1]
         if step.decode and attn_decode_tma_takes(D, nq, nkv, page) and (
                 DECODE_ATTENTION == "tma" or
                 (DECODE_ATTENTION == "auto" and step.n_seqs * nkv >= DECODE_TMA_PAIRS)):
             return attn_decode_tma(q, k_pages, v_pages, block_table, slots=step.slots,
                                    kv_len=step.kv_len, page=page, scale=scale,
-                                   max_kv_len=step.max_kv_len, window=window)
+                                   max_kv_len=step.max_kv_len, window=window, **extra)
         if step.decode:
             return attn_decode_bf16(q, k_pages, v_pages, block_table, slots=step.slots,
                                     kv_len=step.kv_len, page=page, scale=scale,
-                                    max_kv_len=step.max_kv_len, window=window)
+                                    max_kv_len=step.max_kv_len, window=window, **extra)
         # the grid comes from the host's copy of the lengths; a captured step has
         # none, and the kernels then take the most blocks its rows can make
         if PREFILL_ATTENTION == "tc" and attn_prefill_tc_takes(D, nq, k_pages.shape[1], page):
             return attn_prefill_tc(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
                                    slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
-                                   page=page, scale=scale, window=window)
+                                   page=page, scale=scale, window=window, **extra)
         return attn_prefill_bf16(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
                                  slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
-                                 page=page, scale=scale, window=window)
+                                 page=page, scale=scale, window=window, **extra)
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
                         window=window, softcap=softcap, sinks=sinks)

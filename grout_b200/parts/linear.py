@@ -103,5 +103,20 @@ class Linear:
         return ops.silu_mul(self(x), interleave)
 
     def relu_squared(self, x: torch.Tensor) -> torch.Tensor:
-        """max(x W^T, 0)^2, squared before the rounding to the compute dtype."""
+        """max(x W^T, 0)^2.  Where the product's kernel has the epilogue (the tcgen05
+        kernels), the square is taken on the 32-bit sums and rounded once; the pair
+        product takes a prompt's rows under the rule of the fused gate|up product
+        (``ops.gemm_tc2_pays``): fusing saves the same pass over the activations."""
+        w = self.weight
+        if w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.in_features % 8 == 0:
+            if x.shape[0] <= ops.SKINNY_MAX_ROWS:
+                if self.decode_kernel == "tc":
+                    return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, relu_squared=True)
+            elif self.prefill_kernel == "tc":
+                return ops.gemm_tc_bf16(x, w, x.dtype, swap=False, relu_squared=True)
+            elif ops.gemm_tc2_takes(self.out_features, x.dtype) and (
+                    self.prefill_kernel == "pair" or
+                    (self.prefill_kernel == "auto" and
+                     ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True))):
+                return ops.gemm_tc2_bf16(x, w, x.dtype, relu_squared=True)
         return ops.relu_squared(self(x))
