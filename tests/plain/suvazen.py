@@ -107,6 +107,7 @@ def attention_mixer(h, w, prefix, m, positions):
     ``mixer`` object of config.json."""
     T = h.shape[0]
     H, G, D = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
+    h = h.to(DT)
     q = (h @ w[prefix + "q"].to(DT).T).reshape(T, H, D)
     k = (h @ w[prefix + "k"].to(DT).T).reshape(T, G, D)
     v = k
@@ -123,7 +124,7 @@ def attention_mixer(h, w, prefix, m, positions):
 
 def relu_squared_ff(h, w_up, w_down):
     """W_down (max(W_up h, 0))^2."""
-    u = torch.clamp(h @ w_up.to(DT).T, min=0.0)
+    u = torch.clamp(h.to(DT) @ w_up.to(DT).T, min=0.0)
     return (u * u) @ w_down.to(DT).T
 
 
