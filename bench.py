@@ -21,6 +21,10 @@ weights, far more than the 126 MB L2, so nothing is flushed between timed steps.
                                        decode steps (launched one by one, an event pair
                                        around each): calls, time, GB/s, TFLOP/s, fractions
     python bench.py --requests S       the reference's request grid
+    python bench.py --designs [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
+                                       prefill and decode throughput of the Suvazen design beside
+                                       the Qwen3 decoder at equal layer sizes (random weights), and
+                                       with --design-ops the per-kernel tables of both
 """
 import argparse
 import json
@@ -167,6 +171,148 @@ def run_requests(size: str, reps: int) -> int:
                       "unit": "tok/s", "dtype": "bf16", "data": "synthetic", "reps": reps,
                       "layers": cfg["num_hidden_layers"], "cells": cells}))
     return 0
+
+
+# Layer sizes for --designs: (width, query heads, kv heads, head size, gated feed-forward rows,
+# layers, vocabulary).  The Suvazen model of a size has the same width, heads and layers, a
+# feed-forward of 3/2 the rows (two matrices instead of three: the same weights), a rotation of
+# half of every head with scaled frequencies, capped scores, sinks, no window (the same keys
+# as the Qwen3 model sees), one pass over layers 1-2 with its added vector, capped logits.
+DESIGN_SIZES = {"1b": (2048, 16, 8, 128, 6144, 16, 65536),
+                "4b": (2560, 32, 8, 128, 9728, 36, 151936),
+                "8b": (4096, 32, 8, 128, 12288, 36, 151936)}
+
+
+def design_configs(size: str):
+    W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
+    qwen = dict(QWEN3_4B, hidden_size=W, num_attention_heads=nq, num_key_value_heads=nkv, head_dim=D,
+                intermediate_size=I, num_hidden_layers=L, vocab_size=V, tie_word_embeddings=False)
+    mixer = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, softcap=30.0,
+                 rot={"dims": D // 2, "base": 1000000.0,
+                      "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    suv = dict(architecture="Suvazen", vocab=V, width=W, norm={"eps": 1e-5}, residual_mult=0.7,
+               logit_scale=0.5, logit_softcap=30.0, loop={"start": 1, "stop": 3, "times": 1},
+               layers=[dict(type="attention", mixer=mixer, mlp={"kind": "dense", "ff": 3 * I // 2})
+                       for _ in range(L)])
+    return {"qwen3": qwen, "suvazen": suv}
+
+
+def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) -> int:
+    """Prefill of one 2,048-token prompt and decode steps of ``batch`` sequences that hold such
+    prompts, for both designs at each size: device times between CUDA events, the prompt step
+    as the median of six after three, the decode steps as generation runs them (tokens chosen
+    on the device feed the next captured step).  Weights (GBs) dwarf the L2, nothing is flushed."""
+    import torch
+    from grout_b200.engine import Engine
+    from grout_b200.kernels import ops
+    out = {}
+    for size in sizes:
+        out[size] = {}
+        for design, cfg in design_configs(size).items():
+            V = cfg.get("vocab_size", cfg.get("vocab"))
+            room = (PROMPT + warm + steps + 64 + 63) // 64 * 64
+            eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * room, max_batch=batch,
+                                max_seq_len=CONTEXT)
+            g = torch.Generator().manual_seed(1)
+
+            def prompt():
+                return torch.randint(0, V, (PROMPT,), generator=g).tolist()
+
+            times = []
+            for i in range(9):
+                s = eng.open_sequence()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                eng.step([(s, prompt())], [[PROMPT - 1]])
+                b.record()
+                torch.cuda.synchronize()
+                eng.close_sequence(s)
+                if i >= 3:
+                    times.append(a.elapsed_time(b))
+            pre_ms = statistics.median(times)
+            slots = [eng.open_sequence() for _ in range(batch)]
+            for i in range(0, batch, 8):
+                eng.step([(s, prompt()) for s in slots[i:i + 8]])
+            first = torch.randint(0, V, (batch,), generator=g).tolist()
+            logits = eng.step([(s, [first[j]]) for j, s in enumerate(slots)], [[0]] * batch)
+            torch.cuda.synchronize()
+            time.sleep(SETTLE_S)
+            greedy = [eng.default_sampling()] * batch
+            entries = [(s, j) for j, s in enumerate(slots)]
+            for i in range(warm):
+                logits = eng.step_ahead(entries, eng.choose_ahead(logits, greedy, [0.0] * batch))
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(steps):
+                logits = eng.step_ahead(entries, eng.choose_ahead(logits, greedy, [0.0] * batch))
+            b.record()
+            torch.cuda.synchronize()
+            dec_ms = a.elapsed_time(b) / steps
+            n_weights = sum(t.numel() for t in _weights_of(eng))
+            kv_bytes = sum(st.k[:, :1].numel() * 2 * 2 // 64 for st in eng.cache.stores if hasattr(st, "k"))
+            step_bytes = 2 * n_weights + batch * (PROMPT + warm + steps / 2) * kv_bytes
+            out[size][design] = {
+                "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PROMPT / pre_ms * 1e3, 1),
+                "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1),
+                "weights_gb": round(2 * n_weights / 1e9, 2),
+                "decode_hbm_frac": round(step_bytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            if with_ops:
+                for s in slots:
+                    eng.close_sequence(s)
+                slots = [eng.open_sequence() for _ in range(batch)]
+                eng.use_graphs = False
+                for what in ("prompt step", "decode step"):
+                    if what == "decode step":
+                        for s in slots:
+                            eng.close_sequence(s)
+                        slots = [eng.open_sequence() for _ in range(batch)]
+                        eng.step([(s, prompt()) for s in slots])
+                    run = (lambda: eng.step([(slots[0], prompt())], [[PROMPT - 1]])) if what == "prompt step" \
+                        else (lambda: eng.step([(s, [1]) for s in slots], [[0]] * batch))
+                    run()
+                    if what == "prompt step":
+                        eng.close_sequence(slots[0])
+                        slots[0] = eng.open_sequence()
+                    prof = ops.OpProfile(pk["hbm_gbs"], pk["bf16_tflops"])
+                    ops.set_profile(prof)
+                    run()
+                    ops.set_profile(None)
+                    print(f"== {design} at the {size} sizes, {what}" +
+                          (f" of {PROMPT} tokens" if what == "prompt step" else
+                           f", batch {batch}, {PROMPT} keys a sequence") +
+                          f" (peaks: {pk['source']}, {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s)")
+                    print(prof.report())
+            eng.check()
+            del eng, logits
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "prefill and decode throughput, Suvazen beside Qwen3 at equal layer sizes",
+                      "unit": "tok/s", "dtype": "bf16", "data": "synthetic", "batch": batch,
+                      "prompt_len": PROMPT, "steps": steps, "warmup": warm, "peaks": pk["source"],
+                      "sizes": out}))
+    return 0
+
+
+def _weights_of(eng):
+    """Every tensor a step of the engine's model reads as a weight, once."""
+    seen, out = set(), []
+
+    def walk(part):
+        for v in vars(part).values():
+            ts = [v] if hasattr(v, "data_ptr") else ([v.weight] if hasattr(v, "weight") and
+                                                     hasattr(getattr(v, "weight"), "data_ptr") else [])
+            for t in ts:
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    out.append(t)
+        for c in part.children():
+            walk(c)
+
+    for top in [eng.model.embedding, *eng.model.blocks, eng.model.final_norm, eng.model.head]:
+        walk(top)
+    emb = eng.model.embedding.weight
+    return [t for t in out if t.data_ptr() != emb.data_ptr() or getattr(eng.model.head, "tied", False)]
 
 
 def quartiles(xs):
@@ -319,6 +465,13 @@ def main() -> int:
     ap.add_argument("--ops", action="store_true",
                     help="instead of the default run: the per-kernel table of a prompt step and of "
                          "decode steps at --size and --batch")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the default run: the Suvazen design beside the Qwen3 decoder at "
+                         "equal layer sizes (--design-sizes), prefill and decode at --batch")
+    ap.add_argument("--design-sizes", default="1b,4b,8b",
+                    help=f"which of {sorted(DESIGN_SIZES)} --designs runs")
+    ap.add_argument("--design-ops", action="store_true",
+                    help="with --designs: also the per-kernel tables of a prompt step and a decode step")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -331,6 +484,13 @@ def main() -> int:
         return 2
     if args.requests:
         return run_requests(args.requests, max(1, args.reps))
+    if args.designs:
+        sizes = [x for x in args.design_sizes.split(",") if x]
+        if any(x not in DESIGN_SIZES for x in sizes):
+            print(f"bench.py: --design-sizes takes {sorted(DESIGN_SIZES)}", file=sys.stderr)
+            return 2
+        return run_designs(sizes, args.batch, min(args.steps, 64), max(args.warmup, 3), args.design_ops,
+                           peaks())
     if args.prompt_len != PROMPT:
         if not 1 <= args.prompt_len <= 36864:
             print("bench.py: --prompt-len must be 1..36864", file=sys.stderr)

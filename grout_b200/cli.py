@@ -27,7 +27,7 @@ def apply_chat_template(prompt: str) -> str:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="grout_b200", description="Qwen3 dense text generation on one B200")
+    ap = argparse.ArgumentParser(prog="grout_b200", description="Text generation on one B200 with the architecture that the model folder's config.json names")
     ap.add_argument("--model", required=True,
                     help="model folder (config.json, safetensors), or random:CONFIG.json for "
                          "random weights made on the device from --seed (with --prompt-ids)")
