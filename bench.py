@@ -259,8 +259,13 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) ->
                 "weights_gb": round(2 * n_weights / 1e9, 2),
                 "decode_hbm_frac": round(step_bytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
             if with_ops:
-                for s in slots:
-                    eng.close_sequence(s)
+                # a fresh engine: its first captured step is the one the timeline traces
+                eng.check()
+                del eng, logits
+                torch.cuda.empty_cache()
+                eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * room, max_batch=batch,
+                                    max_seq_len=CONTEXT)
+                logits = None
                 slots = [eng.open_sequence() for _ in range(batch)]
                 eng.use_graphs = False
                 for what in ("prompt step", "decode step"):
@@ -284,6 +289,8 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) ->
                            f", batch {batch}, {PROMPT} keys a sequence") +
                           f" (peaks: {pk['source']}, {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s)")
                     print(prof.report())
+                print(f"== {design} at the {size} sizes")
+                print(decode_timeline(eng, slots, V, g, pk))
             eng.check()
             del eng, logits
             torch.cuda.empty_cache()
@@ -412,7 +419,7 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
         print(f"bench.py: {len(labels)} launches were logged for a step of {len(ev) // n} kernels; "
               f"rows are named by kernel", file=sys.stderr)
     kv = sum(eng.cache.length[s] for s in slots)
-    cfg = eng.config
+    kv_spec = next((st.spec for st in eng.cache.stores if hasattr(st, "k")), None)
 
     def must_read(name):
         """Bytes a call of this kernel has to read: a product its weights, the decode
@@ -422,7 +429,7 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
             rows_w, cols_w = part[1].split("x")
             return 2.0 * int(rows_w) * int(cols_w)
         if part[0].startswith("attn_decode") and "second" not in name:
-            return 2.0 * kv * 2 * cfg.num_key_value_heads * cfg.head_dim
+            return 2.0 * kv * 2 * kv_spec.n_kv_heads * kv_spec.head_dim
         return None
 
     lines = [f"== decode step, batch {batch}, {kv // batch} keys a sequence, as it ran inside the captured "

@@ -909,6 +909,24 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
     pl.blocks = tiles * args->split_k;
     pl.lead_share = 0;
   }
+  if (args->silu == 2 && args->split_k == 0) {
+    // An epilogue that is not linear needs the finished sums, so K cannot be cut and its
+    // parts handed on.  With fewer tiles than SMs the even deal above shares nearly every
+    // tile between two blocks, and the store, fence, count and re-read of the partial tiles
+    // cost more than the idle SMs: a block streams at the rate its stages in flight allow,
+    // whoever else runs.  One whole tile per block from half as many tiles as SMs on
+    // (measured inside the decode step, 14,592 x 2,560 at batch 8: see the design notes).
+    int err = 0;
+    const int sms = tc_sms(&err);
+    const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
+#ifndef TC_ACT_WHOLE_FROM
+#define TC_ACT_WHOLE_FROM 2
+#endif
+    if (!err && tiles <= sms && TC_ACT_WHOLE_FROM * tiles >= sms) {
+      pl.blocks = tiles;
+      pl.lead_share = 0;
+    }
+  }
   CUtensorMap ma, mb;
   e = make_map(&ma, A, args->rowsA, args->K, TC_BM);
   if (e) return e;

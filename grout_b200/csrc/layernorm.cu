@@ -13,8 +13,16 @@
 // the final norm), else r.  Means and variances are taken in two passes over
 // values that stay in registers (or are recomputed), all in 32-bit; the block's
 // tree of sums depends on the width only, so a row's result does not depend on
-// the step it is part of.  Norm weights, biases and the offset are 32-bit.
+// the step it is part of (the kernels for bfloat16 activations take a row's sum
+// and sum of squares together instead, see below).  Norm weights, biases and the
+// offset are 32-bit.
+#include <cooperative_groups.h>
+
+#include <type_traits>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 struct LayerNormArgs {
   const float* res_in;
@@ -38,7 +46,7 @@ struct LayerNormArgs {
   int n_rows, N;
 };
 
-#define LN_VMAX 4   // float4 pieces per thread in the register kernel
+#define LN_VMAX_MOST 4   // float4 pieces per thread in the register kernel, at most
 
 template <typename T> struct LnVec;
 template <> struct LnVec<float> {
@@ -66,28 +74,37 @@ template <> struct LnVec<bf16> {
   }
 };
 
-// Widths that are a multiple of 4 and at most 4 * 1024 * LN_VMAX: a thread keeps
-// its values in registers from the first load to the last store.
-template <typename T>
-__global__ void add_layernorm_vec_kernel(const LayerNormArgs a) {
-  __shared__ float scratch[32];
+// Block-wide sums of two values at once with a fixed tree (one pair of barriers).
+__device__ __forceinline__ float2 block_sum2(float x, float y, float2* scratch2) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  x = warp_sum(x), y = warp_sum(y);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch2[warp] = make_float2(x, y);
+  __syncthreads();
+  float2 r = (lane < nwarps) ? scratch2[lane] : make_float2(0.f, 0.f);
+  r.x = warp_sum(r.x), r.y = warp_sum(r.y);
+  return r;
+}
+
+// Widths that are a multiple of 4 and at most 16,384: a thread keeps its values
+// (LN_VMAX pieces of four) in registers from the first load to the last store.
+// The kernel is a chain of dependent steps (loads, the sums over the row, stores),
+// so what it reaches is set by how many rows an SM has in flight: blocks are kept
+// small (a row of 2,560 is 160 threads with four pieces each) and norm weights are
+// read where they are used, not held from the start, which keeps the registers
+// at 64 a thread and six or more rows on an SM.  (One piece a thread, 640 threads
+// and weights held in registers left one row on an SM: 2.6 times the time.)
+// In 32-bit the mean is taken first and the deviations are squared (two sums per
+// norm); with bfloat16 activations sum and sum of squares are taken together (one
+// sum per norm, var = E[x^2] - mean^2 in 32-bit), which halves the chain.
+template <typename T, int LN_VMAX>
+__global__ void __launch_bounds__(1024) add_layernorm_vec_kernel(const LayerNormArgs a) {
+  __shared__ float2 scratch2[32];
+  float* scratch = reinterpret_cast<float*>(scratch2);
+  constexpr bool TWO_PASS = std::is_same<T, float>::value;
   pdl_launch_dependents_if_small();
   const int N = a.N;
-  // weights, biases and the offset are no kernel's output: fetched before the wait
-  float wv[LN_VMAX][4], bv[LN_VMAX][4], pw[LN_VMAX][4], pb[LN_VMAX][4], ov[LN_VMAX][4];
-#pragma unroll
-  for (int j = 0; j < LN_VMAX; ++j) {
-    const int i = (threadIdx.x + j * blockDim.x) * 4;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) wv[j][e] = pw[j][e] = 1.f, bv[j][e] = pb[j][e] = ov[j][e] = 0.f;
-    if (i < N) {
-      if (a.w) LnVec<float>::load(a.w + i, wv[j]);
-      if (a.b) LnVec<float>::load(a.b + i, bv[j]);
-      if (a.post_w) LnVec<float>::load(a.post_w + i, pw[j]);
-      if (a.post_b) LnVec<float>::load(a.post_b + i, pb[j]);
-      if (a.offset) LnVec<float>::load(a.offset + i, ov[j]);
-    }
-  }
   pdl_wait();
   const int r = blockIdx.x;
   const size_t s = a.rows ? (size_t)a.rows[r] : (size_t)r;
@@ -129,42 +146,54 @@ __global__ void add_layernorm_vec_kernel(const LayerNormArgs a) {
     }
   }
   const float inv_n = 1.0f / (float)N;
-  if (has_d && a.post_w) {
-    float mean = 0.f;
-    if (a.post_center) {
-      float sm = 0.f;
-#pragma unroll
-      for (int j = 0; j < LN_VMAX; ++j)
-        if ((threadIdx.x + j * blockDim.x) * 4 < N) sm += (dv[j][0] + dv[j][1]) + (dv[j][2] + dv[j][3]);
-      mean = block_sum(sm, scratch) * inv_n;
-    }
-    float sq = 0.f;
+  // mean and 1 / sqrt(var + eps) of the row whose pieces are x
+  auto row_stats = [&](const float (&x)[LN_VMAX][4], bool center, float eps, float& mean, float& rstd) {
+    float sm = 0.f, sq = 0.f;
 #pragma unroll
     for (int j = 0; j < LN_VMAX; ++j)
       if ((threadIdx.x + j * blockDim.x) * 4 < N) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          dv[j][e] -= mean;
-          sq += dv[j][e] * dv[j][e];
-        }
+        sm += (x[j][0] + x[j][1]) + (x[j][2] + x[j][3]);
+        if (!TWO_PASS) sq += (x[j][0] * x[j][0] + x[j][1] * x[j][1]) + (x[j][2] * x[j][2] + x[j][3] * x[j][3]);
       }
-    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) * inv_n + a.post_eps);
+    if (TWO_PASS) {
+      mean = center ? block_sum(sm, scratch) * inv_n : 0.f;
 #pragma unroll
-    for (int j = 0; j < LN_VMAX; ++j)
+      for (int j = 0; j < LN_VMAX; ++j)
+        if ((threadIdx.x + j * blockDim.x) * 4 < N) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) dv[j][e] = dv[j][e] * rstd * pw[j][e] + pb[j][e];
+          for (int e = 0; e < 4; ++e) sq += (x[j][e] - mean) * (x[j][e] - mean);
+        }
+      rstd = 1.0f / sqrtf(block_sum(sq, scratch) * inv_n + eps);
+    } else {
+      const float2 t = block_sum2(sm, sq, scratch2);
+      mean = center ? t.x * inv_n : 0.f;
+      rstd = 1.0f / sqrtf(fmaxf(t.y * inv_n - mean * mean, 0.f) + eps);
+    }
+  };
+  if (has_d && a.post_w) {
+    float mean, rstd;
+    row_stats(dv, a.post_center != 0, a.post_eps, mean, rstd);
+#pragma unroll
+    for (int j = 0; j < LN_VMAX; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      if (i < N) {
+        float pw[4], pb[4] = {0.f, 0.f, 0.f, 0.f};
+        LnVec<float>::load(a.post_w + i, pw);
+        if (a.post_b) LnVec<float>::load(a.post_b + i, pb);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dv[j][e] = (dv[j][e] - mean) * rstd * pw[e] + pb[e];
+      }
+    }
   }
   float* rout = a.res_out ? a.res_out + (size_t)r * N : nullptr;
-  float sm = 0.f;
 #pragma unroll
   for (int j = 0; j < LN_VMAX; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < N) {
+      float ov[4] = {0.f, 0.f, 0.f, 0.f};
+      if (a.offset) LnVec<float>::load(a.offset + i, ov);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        av[j][e] = av[j][e] + (has_d ? a.mult * dv[j][e] : 0.f) + ov[j][e];
-        sm += av[j][e];
-      }
+      for (int e = 0; e < 4; ++e) av[j][e] = av[j][e] + (has_d ? a.mult * dv[j][e] : 0.f) + ov[e];
       if (rout) LnVec<float>::store(rout + i, av[j]);
     }
   }
@@ -172,29 +201,123 @@ __global__ void add_layernorm_vec_kernel(const LayerNormArgs a) {
     pdl_launch_dependents_if_large();
     return;
   }
-  const float mean = a.center ? block_sum(sm, scratch) * inv_n : 0.f;
-  float sq = 0.f;
-#pragma unroll
-  for (int j = 0; j < LN_VMAX; ++j)
-    if ((threadIdx.x + j * blockDim.x) * 4 < N) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        av[j][e] -= mean;
-        sq += av[j][e] * av[j][e];
-      }
-    }
-  const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) * inv_n + a.eps);
+  float mean, rstd;
+  row_stats(av, a.center != 0, a.eps, mean, rstd);
   pdl_launch_dependents_if_large();
   T* yo = (T*)a.y + (size_t)r * N;
 #pragma unroll
   for (int j = 0; j < LN_VMAX; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < N) {
-      float o[4];
+      float wv[4], bv[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+      LnVec<float>::load(a.w + i, wv);
+      if (a.b) LnVec<float>::load(a.b + i, bv);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = av[j][e] * rstd * wv[j][e] + bv[j][e];
+      for (int e = 0; e < 4; ++e) o[e] = (av[j][e] - mean) * rstd * wv[e] + bv[e];
       LnVec<T>::store(yo + i, o);
     }
+  }
+}
+
+// A handful of rows (a decode step) would keep a handful of SMs busy, each with a
+// long chain of dependent loads.  Here a cluster of LN_CLUSTER blocks shares a
+// row: each block owns a quarter of the columns, takes the mean and the sum of
+// squared deviations of its quarter, and the quarters' pairs meet through
+// distributed shared memory, where they are combined exactly (the mean of the
+// means; the sums of squares plus each quarter's n (mean_q - mean)^2), in rank
+// order.  One cluster barrier per norm; no block spins on memory.
+#define LN_CLUSTER 4
+template <typename T>
+__global__ void add_layernorm_cluster_kernel(const LayerNormArgs a) {
+  __shared__ float scratch[32];
+  __shared__ float stat[2][LN_CLUSTER][2];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  pdl_launch_dependents_if_small();
+  const int N = a.N, cols = N / LN_CLUSTER;       // a multiple of 4
+  const int i = rank * cols + threadIdx.x * 4;    // this thread's four columns
+  const bool active = threadIdx.x * 4 < cols;
+  float wv[4] = {1.f, 1.f, 1.f, 1.f}, bv[4] = {0.f, 0.f, 0.f, 0.f}, pw[4] = {1.f, 1.f, 1.f, 1.f},
+        pb[4] = {0.f, 0.f, 0.f, 0.f}, ov[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {   // no kernel's output: before the wait
+    if (a.w) LnVec<float>::load(a.w + i, wv);
+    if (a.b) LnVec<float>::load(a.b + i, bv);
+    if (a.post_w) LnVec<float>::load(a.post_w + i, pw);
+    if (a.post_b) LnVec<float>::load(a.post_b + i, pb);
+    if (a.offset) LnVec<float>::load(a.offset + i, ov);
+  }
+  pdl_wait();
+  const int r = blockIdx.x / LN_CLUSTER;
+  const size_t s = a.rows ? (size_t)a.rows[r] : (size_t)r;
+  const bool has_d = a.delta || a.parts;
+  float av[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    if (a.res_in) LnVec<float>::load(a.res_in + s * N + i, av);
+    if (a.delta) LnVec<T>::load((const T*)a.delta + s * N + i, dv);
+    // eight partials are requested at once and then added in order (a product is split at
+    // most eight ways, so this is one trip to L2)
+    for (int k0 = 0; k0 < a.n_parts; k0 += 8) {
+      float pk[8][4];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + u < a.n_parts ? k0 + u : a.n_parts - 1;
+        LnVec<float>::load(a.parts + (size_t)k * a.part_stride + s * N + i, pk[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (k0 + u < a.n_parts) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dv[e] += pk[u][e];
+        }
+    }
+  }
+  // mean and 1 / sqrt(var + eps) of the whole row from this block's quarter x[0..3]
+  auto row_stats = [&](int round, const float (&x)[4], bool center, float eps, float& mean, float& rstd) {
+    float mean_q = 0.f;
+    if (center) mean_q = block_sum(active ? (x[0] + x[1]) + (x[2] + x[3]) : 0.f, scratch) / (float)cols;
+    float sq = 0.f;
+    if (active) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sq += (x[e] - mean_q) * (x[e] - mean_q);
+    }
+    const float m2_q = block_sum(sq, scratch);
+    // every block puts its pair into every block's table (thread k writes to block k): after
+    // the one barrier each block reads its own shared memory only
+    if (threadIdx.x < LN_CLUSTER) {
+      float* dst = cluster.map_shared_rank(&stat[round][0][0], threadIdx.x);
+      dst[rank * 2] = mean_q;
+      dst[rank * 2 + 1] = m2_q;
+    }
+    cluster.sync();
+    float msum = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_CLUSTER; ++k) msum += stat[round][k][0];
+    mean = msum / (float)LN_CLUSTER;
+    float m2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_CLUSTER; ++k) {
+      const float dm = stat[round][k][0] - mean;
+      m2 += stat[round][k][1] + (float)cols * dm * dm;
+    }
+    rstd = 1.0f / sqrtf(m2 / (float)N + eps);
+  };
+  if (has_d && a.post_w) {   // (the same for every block of the cluster)
+    float mean, rstd;
+    row_stats(0, dv, a.post_center != 0, a.post_eps, mean, rstd);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dv[e] = (dv[e] - mean) * rstd * pw[e] + pb[e];
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) av[e] = av[e] + (has_d ? a.mult * dv[e] : 0.f) + ov[e];
+  if (active && a.res_out) LnVec<float>::store(a.res_out + (size_t)r * N + i, av);
+  if (!a.w) return;
+  float mean, rstd;
+  row_stats(1, av, a.center != 0, a.eps, mean, rstd);
+  if (active) {
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = (av[e] - mean) * rstd * wv[e] + bv[e];
+    LnVec<T>::store((T*)a.y + (size_t)r * N + i, o);
   }
 }
 
@@ -283,13 +406,29 @@ static int launch(const LayerNormArgs& a, cudaStream_t stream) {
                         (uintptr_t)a.post_w | (uintptr_t)a.post_b | (uintptr_t)a.offset |
                         (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.res_out | (uintptr_t)a.y |
                         (uintptr_t)(a.part_stride * 4);
-  if (a.N % 4 == 0 && a.N <= 4 * 1024 * LN_VMAX && (all & 15) == 0 &&
-      ((size_t)a.N * sizeof(T)) % 8 == 0) {
-    int threads = (a.N / 4 + LN_VMAX - 1) / LN_VMAX;
+  const bool vec_ok = a.N % 4 == 0 && (all & 15) == 0 && ((size_t)a.N * sizeof(T)) % 8 == 0;
+  // The cluster kernel is chosen by the number of rows and sums in another order than
+  // the kernels below.  The 32-bit path never takes it: there the order of a row's sums
+  // may depend on the width alone, so that a token's result is the same in a step of one
+  // row and in a step of thousands.
+  constexpr bool by_rows_too = !std::is_same<T, float>::value;
+  if (by_rows_too && vec_ok && a.n_rows <= 64 && a.N >= 1024 && a.N % (4 * LN_CLUSTER) == 0 &&
+      a.N / LN_CLUSTER <= 4096) {
+    const int threads = ((a.N / LN_CLUSTER / 4 + 31) / 32) * 32;
+    return gb_launch_cluster(add_layernorm_cluster_kernel<T>, dim3(a.n_rows * LN_CLUSTER), dim3(threads),
+                             0, stream, LN_CLUSTER, a);
+  }
+  if (vec_ok && a.N <= 4 * 1024 * LN_VMAX_MOST) {
+    const int vmax = a.N <= 1024 ? 1 : (a.N <= 2048 ? 2 : 4);
+    int threads = (a.N / 4 + vmax - 1) / vmax;
     threads = ((threads + 31) / 32) * 32;
     if (threads < 64) threads = 64;
     if (threads > 1024) threads = 1024;
-    return gb_launch(add_layernorm_vec_kernel<T>, dim3(a.n_rows), dim3(threads), 0, stream, a);
+    switch (vmax) {
+      case 1: return gb_launch(add_layernorm_vec_kernel<T, 1>, dim3(a.n_rows), dim3(threads), 0, stream, a);
+      case 2: return gb_launch(add_layernorm_vec_kernel<T, 2>, dim3(a.n_rows), dim3(threads), 0, stream, a);
+      default: return gb_launch(add_layernorm_vec_kernel<T, 4>, dim3(a.n_rows), dim3(threads), 0, stream, a);
+    }
   }
   int threads = ((a.N + 3) / 4 + 31) / 32 * 32;
   if (threads < 32) threads = 32;

@@ -21,10 +21,10 @@ def _ops():
 
 # ------------------------------------------------------------------ add + layer norm
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("N", [200, 203, 2560, 5000])
-def test_add_layernorm_every_form(dtype, N):
+@pytest.mark.parametrize("rows", [9, 100])      # few rows of a wide model share a row among blocks
+@pytest.mark.parametrize("N", [200, 203, 2560, 5000, 12000])
+def test_add_layernorm_every_form(dtype, N, rows):
     dt = DT[dtype]
-    rows = 9
     res = _rand((rows, N), torch.float32, 3, 2.0)
     delta = _rand((rows, N), dt, 4) + 0.3                         # a mean that is not zero
     w, b = 1 + 0.1 * _rand((N,), torch.float32, 5), 0.2 * _rand((N,), torch.float32, 6)
