@@ -177,7 +177,7 @@ def run_requests(size: str, reps: int) -> int:
 # layers, vocabulary).  The Suvazen model of a size has the same width, heads and layers, a
 # feed-forward of 3/2 the rows (two matrices instead of three: the same weights), a rotation of
 # half of every head with scaled frequencies, capped scores, sinks, no window (the same keys
-# as the Qwen3 model sees), one pass over layers 1-2 with its added vector, capped logits.
+# as the Qwen3 model sees), one pass over layers 2-3 with its added vector, capped logits.
 DESIGN_SIZES = {"1b": (2048, 16, 8, 128, 6144, 16, 65536),
                 "4b": (2560, 32, 8, 128, 9728, 36, 151936),
                 "8b": (4096, 32, 8, 128, 12288, 36, 151936)}
@@ -190,8 +190,8 @@ def design_configs(size: str):
     mixer = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, softcap=30.0,
                  rot={"dims": D // 2, "base": 1000000.0,
                       "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
-    suv = dict(architecture="Suvazen", vocab=V, width=W, norm={"eps": 1e-5}, residual_mult=0.7,
-               logit_scale=0.5, logit_softcap=30.0, loop={"start": 1, "stop": 3, "times": 1},
+    suv = dict(architecture="Suvazen", vocab=V, width=W, norm={"eps": 1e-6}, residual_mult=0.8,
+               logit_scale=0.25, logit_softcap=30.0, loop={"start": 2, "stop": 4, "times": 1},
                layers=[dict(type="attention", mixer=mixer, mlp={"kind": "dense", "ff": 3 * I // 2})
                        for _ in range(L)])
     return {"qwen3": qwen, "suvazen": suv}

@@ -438,3 +438,51 @@ def test_prompt_products_square_the_relu(kernel, M, N, K):
     ops.check_kernel_errors()
     want = plain.relu_squared_ff(x.double(), w, torch.eye(N, dtype=torch.float64))
     assert torch.allclose(got.cpu().double(), want, atol=2e-3 * float(want.abs().max()), rtol=2e-2)
+
+
+# ------------------------------------------------------------------ contributions through any norm
+@pytest.mark.parametrize("dtype", list(DT))
+def test_a_contribution_through_norms_with_and_without_a_kernel_for_it(dtype):
+    """A sublayer's output on its way into the stream (its own norm, a factor, an
+    offset): ``LayerNorm`` takes it whole, ``RMSNorm`` and a mixed pair resolve it
+    step by step; all agree with the plain arithmetic."""
+    from grout_b200.parts import BuildContext, Contribution, PartSpec, build_part
+    dt = DT[dtype]
+    ctx = BuildContext(dt, torch.device(DEV))
+    N, T = 256, 5
+    ln_a = build_part("norm", PartSpec("layernorm", dict(dim=N, eps=1e-5)), ctx)
+    ln_b = build_part("norm", PartSpec("layernorm", dict(dim=N, eps=2e-5)), ctx)
+    rms = build_part("norm", PartSpec("rmsnorm", dict(dim=N, eps=1e-6)), ctx)
+    wa, ba = 1 + 0.1 * _rand((N,), torch.float32, 1), 0.1 * _rand((N,), torch.float32, 2)
+    wb, bb = 1 + 0.1 * _rand((N,), torch.float32, 3), 0.1 * _rand((N,), torch.float32, 4)
+    wr = 1 + 0.1 * _rand((N,), torch.float32, 5)
+    ln_a.load({"weight": wa.to(DEV), "bias": ba.to(DEV)})
+    ln_b.load({"weight": wb.to(DEV), "bias": bb.to(DEV)})
+    rms.load({"weight": wr.to(dt).to(DEV)})
+    wr = wr.to(dt)
+    res, delta = _rand((T, N), torch.float32, 6), _rand((T, N), dt, 7)
+    off = _rand((N,), torch.float32, 8)
+    tol = dict(atol=8 * _eps(dt), rtol=4 * _eps(dt))
+
+    def rms_plain(x):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6) * wr.double()
+
+    # layer norm behind, layer norm in front: one kernel
+    want = res.double() + 0.6 * plain.layer_norm(delta.double(), wb, bb, 2e-5) + off.double()
+    r, y = ln_a.add_norm(res.clone().to(DEV), Contribution(delta.to(DEV), ln_b, 0.6, off.to(DEV)))
+    assert torch.allclose(r.cpu().double(), want, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(y.cpu().double(), plain.layer_norm(want, wa, ba, 1e-5), **tol)
+    # layer norm behind, RMS norm in front: resolved, then the RMS norm's kernel
+    r, y = rms.add_norm(res.clone().to(DEV), Contribution(delta.to(DEV), ln_b, 0.6, off.to(DEV)))
+    assert torch.allclose(r.cpu().double(), want, atol=4 * _eps(dt), rtol=4 * _eps(dt))
+    assert torch.allclose(y.cpu().double(), rms_plain(want), atol=16 * _eps(dt), rtol=8 * _eps(dt))
+    # RMS norm behind, layer norm in front
+    want = res.double() + 0.6 * rms_plain(delta.double())
+    r, y = ln_a.add_norm(res.clone().to(DEV), Contribution(delta.to(DEV), rms, 0.6))
+    assert torch.allclose(r.cpu().double(), want, atol=4 * _eps(dt), rtol=4 * _eps(dt))
+    assert torch.allclose(y.cpu().double(), plain.layer_norm(want, wa, ba, 1e-5), atol=16 * _eps(dt), rtol=8 * _eps(dt))
+    # no norm behind, only an offset (what a pass's vector is in front of a model's first layer)
+    r, y = ln_a.add_norm(None, Contribution(delta.to(DEV), None, 1.0, off.to(DEV)))
+    want = delta.double() + off.double()
+    assert torch.allclose(r.cpu().double(), want, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(y.cpu().double(), plain.layer_norm(want, wa, ba, 1e-5), **tol)
