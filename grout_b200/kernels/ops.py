@@ -1044,6 +1044,12 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
     return min(s for s, c in cost.items() if c <= 1.03 * best)
 
 
+def _keys_visited(max_kv_len: int, window: Optional[int], page: int) -> int:
+    """The most keys a decode row reads: its sequence's, or with a window the
+    window's, rounded out to the tiles that hold them."""
+    return min(max_kv_len, window + page - 1) if window else max_kv_len
+
+
 @_profiled("attn_decode_bf16", _cost_attention)
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
                      max_kv_len: int, window: Optional[int] = None,
@@ -1061,7 +1067,9 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
         _need(t, nm, torch.int32)
     if slots.shape[0] != B or kv_len.shape[0] != B:
         raise KernelError("one slot and one length per query row are needed")
-    ns = int(n_splits) if n_splits else decode_splits(B, nkv, max_kv_len, q.device)
+    # (a window bounds the keys a row visits, whatever its sequence's length)
+    ns = int(n_splits) if n_splits else decode_splits(B, nkv, _keys_visited(max_kv_len, window, page),
+                                                      q.device)
     out = torch.empty_like(q)
     part_o = part_ml = None
     if ns > 1:
@@ -1158,7 +1166,8 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
         raise KernelError("one slot and one length per query row are needed")
     stages = int(stages or DECODE_TMA_STAGES) or (2 if B * nkv < DECODE_TMA_DEEP_PAIRS else 3)
     per_sm = {2: 3, 3: 2, 4: 1}.get(stages, 2) if D == 128 else 3
-    ns = int(n_splits) if n_splits else decode_tma_splits(B, nkv, max_kv_len, q.device, per_sm)
+    ns = int(n_splits) if n_splits else decode_tma_splits(B, nkv, _keys_visited(max_kv_len, window, page),
+                                                          q.device, per_sm)
     out = torch.empty_like(q)
     a = _DecodeTmaArgs()
     if ns > 1:
