@@ -915,7 +915,8 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
     // tile between two blocks, and the store, fence, count and re-read of the partial tiles
     // cost more than the idle SMs: a block streams at the rate its stages in flight allow,
     // whoever else runs.  One whole tile per block from half as many tiles as SMs on
-    // (measured inside the decode step, 14,592 x 2,560 at batch 8: see the design notes).
+    // (inside the decode step, 14,592 x 2,560 at batch 8 on 148 SMs: 21.0 us exposed with the
+    // even deal, 16.6 us with the 114 whole tiles).
     int err = 0;
     const int sms = tc_sms(&err);
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
