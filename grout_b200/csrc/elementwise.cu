@@ -7,7 +7,14 @@
 // their g ups (the layout the decode product's fused epilogue uses).
 // out[r, i] = g / (1 + exp(-g)) * u in 32-bit, one rounding at the store
 // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
-template <typename T>
+// The gate's activation: 0 = silu, g / (1 + exp(-g)); 1 = the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+template <int ACT> __device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* in, T* __restrict__ out, int I, int group) {
   pdl_launch_dependents_if_small();
   pdl_wait();
@@ -19,11 +26,12 @@ __global__ void silu_mul_kernel(const T* in, T* __restrict__ out, int I, int gro
   const float g = to_f32<T>(in[r * 2 * I + gi]);
   const float u = to_f32<T>(in[r * 2 * I + ui]);
   pdl_launch_dependents_if_large();
-  out[r * I + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  out[r * I + i] = from_f32<T>(gate_act<ACT>(g) * u);
 }
 
 // bf16, eight outputs per thread in 16-byte pieces: for the plain layout and for
 // groups of 8 a thread's gates are 16 contiguous bytes and so are its ups.
+template <int ACT>
 __global__ void silu_mul_vec8_kernel(const bf16* in, bf16* __restrict__ out, int I, int group) {
   pdl_launch_dependents_if_small();
   pdl_wait();
@@ -44,12 +52,12 @@ __global__ void silu_mul_vec8_kernel(const bf16* in, bf16* __restrict__ out, int
   for (int k = 0; k < 4; ++k) {
     const float ga = __low2float(g2[k]), gb = __high2float(g2[k]);
     const float ua = __low2float(u2[k]), ub = __high2float(u2[k]);
-    o2[k] = __floats2bfloat162_rn(ga / (1.0f + expf(-ga)) * ua, gb / (1.0f + expf(-gb)) * ub);
+    o2[k] = __floats2bfloat162_rn(gate_act<ACT>(ga) * ua, gate_act<ACT>(gb) * ub);
   }
   *reinterpret_cast<uint4*>(out + r * (size_t)I + (size_t)v * 8) = o4;
 }
 
-template <typename T>
+template <typename T, int ACT = 0>
 static int silu_mul(const void* in, void* out, int n_rows, int I, int group, cudaStream_t s) {
   if (n_rows < 0 || I <= 0 || group < 0 || (group && I % group)) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
@@ -57,16 +65,16 @@ static int silu_mul(const void* in, void* out, int n_rows, int I, int group, cud
     // rows go to grid.y; split very long steps
     for (int r0 = 0; r0 < n_rows; r0 += 65535) {
       const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
-      int e = silu_mul<T>((const T*)in + (size_t)r0 * 2 * I, (T*)out + (size_t)r0 * I, n, I, group, s);
+      int e = silu_mul<T, ACT>((const T*)in + (size_t)r0 * 2 * I, (T*)out + (size_t)r0 * I, n, I, group, s);
       if (e) return e;
     }
     return 0;
   }
   if (sizeof(T) == 2 && I % 8 == 0 && (group == 0 || group == 8) &&
       ((((uintptr_t)in) | ((uintptr_t)out)) & 15) == 0)
-    return gb_launch(silu_mul_vec8_kernel, dim3((I / 8 + 127) / 128, n_rows), dim3(128), 0, s,
+    return gb_launch(silu_mul_vec8_kernel<ACT>, dim3((I / 8 + 127) / 128, n_rows), dim3(128), 0, s,
                      (const bf16*)in, (bf16*)out, I, group);
-  return gb_launch(silu_mul_kernel<T>, dim3((I + 255) / 256, n_rows), dim3(256), 0, s,
+  return gb_launch(silu_mul_kernel<T, ACT>, dim3((I + 255) / 256, n_rows), dim3(256), 0, s,
                    (const T*)in, (T*)out, I, group);
 }
 GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, int group,
@@ -76,6 +84,15 @@ GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, int 
 GB_EXPORT int gb_silu_mul_bf16(const void* in, void* out, int n_rows, int I, int group,
                                cudaStream_t s) {
   return silu_mul<bf16>(in, out, n_rows, I, group, s);
+}
+// The same with the tanh form of gelu as the gate's activation.
+GB_EXPORT int gb_gelu_tanh_mul_f32(const void* in, void* out, int n_rows, int I, int group,
+                                   cudaStream_t s) {
+  return silu_mul<float, 1>(in, out, n_rows, I, group, s);
+}
+GB_EXPORT int gb_gelu_tanh_mul_bf16(const void* in, void* out, int n_rows, int I, int group,
+                                    cudaStream_t s) {
+  return silu_mul<bf16, 1>(in, out, n_rows, I, group, s);
 }
 
 template <typename TI, typename TO>

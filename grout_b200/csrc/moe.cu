@@ -1,0 +1,289 @@
+// A feed-forward made of many small experts, of which every token uses a few.
+//
+//   z = x Wr^T (32-bit);  s = softmax(z) over all router outputs
+//   choice score c = s + correction;  the outputs form n_groups equal groups of
+//   neighbours, a group's score is its largest c, and only outputs of the
+//   keep_groups best groups can be chosen (the others count as -inf);  the `top`
+//   outputs with the largest c are chosen and weigh in with their s, as it is
+//   expert e < E:   g = min(x Wg_e^T, limit), u = clamp(x Wu_e^T, -limit, limit),
+//                   y = (g sigmoid(slope g) (u + 1)) Wd_e^T
+//   output >= E:    an expert that hands its input on, y = x
+//   out = sum over the chosen of s * y
+//
+// Nothing here needs the host to know how many tokens an expert got, so a step
+// can be captured: `route` chooses and counts, `sort` turns the counts into a
+// list of (token, choice) pairs ordered by expert, and the two products walk
+// tiles of that list; a block finds its expert from the counts, and blocks
+// beyond the last tile return.  A pair's row is computed the same way wherever it
+// lands in the list, so a token's result does not depend on the batch.  The
+// weighted results are left as `top` 32-bit partial sums [top, T, W]
+// (choice j of token t in out[j, t, :]), which the norm that follows adds in
+// order.
+#include "common.cuh"
+
+struct MoeArgs {
+  const void* x;            // [T, W] activations
+  const float* router_w;    // [E + n_identity, W]
+  const float* correction;  // [E + n_identity]
+  const void* w_gate;       // [E, F, W]
+  const void* w_up;         // [E, F, W]
+  const void* w_down;       // [E, W, F]
+  int* ids;                 // [T, top] chosen outputs
+  float* wts;               // [T, top] their scores
+  int* rank;                // [T, top] place of the pair among its expert's pairs
+  int* counts;              // [E] pairs per expert; zero on entry
+  int* offsets;             // [E + 1]
+  int* perm;                // [T top] pairs (t * top + j) ordered by expert
+  void* act;                // [T top, F] activations of the experts' inner layer, in list order
+  float* out;               // [top, T, W]
+  int T, W, F, E, n_identity, top, n_groups, keep_groups;
+  float limit, slope;
+};
+
+#define MOE_MAX_OUTPUTS 1024
+
+template <typename T>
+__global__ void moe_route_kernel(const MoeArgs a) {
+  extern __shared__ float sm[];   // z [n_all], c [n_all]
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int n_all = a.E + a.n_identity, W = a.W;
+  float* z = sm;
+  float* c = sm + n_all;
+  const T* x = (const T*)a.x + (size_t)t * W;
+  for (int e = warp; e < n_all; e += nwarps) {
+    const float* w = a.router_w + (size_t)e * W;
+    float acc = 0.f;
+    for (int i = lane; i < W; i += 32) acc = fmaf(to_f32<T>(x[i]), w[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float mx = -INFINITY, sum = 0.f;
+    for (int e = 0; e < n_all; ++e) mx = fmaxf(mx, z[e]);
+    for (int e = 0; e < n_all; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
+    for (int e = 0; e < n_all; ++e) { z[e] = z[e] / sum; c[e] = z[e] + a.correction[e]; }
+    if (a.n_groups > 1 && a.keep_groups < a.n_groups) {
+      const int per = n_all / a.n_groups;
+      // drop the groups that are not among the best: n_groups - keep_groups times the worst
+      // remaining one (of equal groups the later one goes first)
+      unsigned long long dropped[MOE_MAX_OUTPUTS / 64] = {0};
+      for (int d = 0; d < a.n_groups - a.keep_groups; ++d) {
+        int worst = -1;
+        float worst_v = INFINITY;
+        for (int g = 0; g < a.n_groups; ++g) {
+          if (dropped[g >> 6] >> (g & 63) & 1ull) continue;
+          float best = -INFINITY;
+          for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+          if (best <= worst_v) { worst_v = best; worst = g; }
+        }
+        dropped[worst >> 6] |= 1ull << (worst & 63);
+      }
+      for (int g = 0; g < a.n_groups; ++g)
+        if (dropped[g >> 6] >> (g & 63) & 1ull)
+          for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+    }
+    for (int j = 0; j < a.top; ++j) {   // the largest first; of equal ones the earlier
+      int best = 0;
+      float best_v = -INFINITY;
+      bool found = false;
+      for (int e = 0; e < n_all; ++e)
+        if (!isnan(c[e]) && (!found || c[e] > best_v)) { best = e; best_v = c[e]; found = true; }
+      c[best] = NAN;                    // taken
+      a.ids[(size_t)t * a.top + j] = best;
+      a.wts[(size_t)t * a.top + j] = z[best];
+      a.rank[(size_t)t * a.top + j] = best < a.E ? atomicAdd(&a.counts[best], 1) : -1;
+    }
+  }
+  __syncthreads();
+  pdl_launch_dependents_if_large();
+  for (int j = 0; j < a.top; ++j) {     // experts that hand their input on
+    if (a.ids[(size_t)t * a.top + j] < a.E) continue;
+    const float w = a.wts[(size_t)t * a.top + j];
+    float* o = a.out + ((size_t)j * a.T + t) * W;
+    for (int i = tid; i < W; i += blockDim.x) o[i] = w * to_f32<T>(x[i]);
+  }
+}
+
+__global__ void moe_sort_kernel(const MoeArgs a) {
+  pdl_wait();
+  const int tid = threadIdx.x;
+  if (tid == 0) {          // few experts: a serial scan is shorter than its set-up
+    int run = 0;
+    for (int e = 0; e < a.E; ++e) { a.offsets[e] = run; run += a.counts[e]; }
+    a.offsets[a.E] = run;
+  }
+  __syncthreads();
+  const int n_pairs = a.T * a.top;
+  for (int p = tid; p < n_pairs; p += blockDim.x) {
+    const int e = a.ids[p];
+    if (e < a.E) a.perm[a.offsets[e] + a.rank[p]] = p;
+  }
+  __syncthreads();
+  for (int e = tid; e < a.E; e += blockDim.x) a.counts[e] = 0;   // zero again for the next call
+}
+
+#define MOE_BM 16
+#define MOE_BN 64
+#define MOE_BK 32
+
+// Which expert and which of its tiles of MOE_BM pairs block `b` has; false beyond the last.
+__device__ __forceinline__ bool moe_find_tile(const int* offsets, int E, int b, int& e_out,
+                                              int& first, int& n_rows) {
+  int tiles = 0;
+  for (int e = 0; e < E; ++e) {
+    const int cnt = offsets[e + 1] - offsets[e];
+    const int nt = (cnt + MOE_BM - 1) / MOE_BM;
+    if (b < tiles + nt) {
+      e_out = e;
+      first = offsets[e] + (b - tiles) * MOE_BM;
+      n_rows = min(MOE_BM, offsets[e + 1] - first);
+      return true;
+    }
+    tiles += nt;
+  }
+  return false;
+}
+
+// act[p, f] = fn(x[token(p)] . Wg_e[f], x[token(p)] . Wu_e[f]) for the pairs p of a tile
+template <typename T>
+__global__ void __launch_bounds__(256) moe_up_kernel(const MoeArgs a) {
+  __shared__ float As[MOE_BM][MOE_BK];
+  __shared__ float Gs[MOE_BN][MOE_BK + 1];
+  __shared__ float Us[MOE_BN][MOE_BK + 1];
+  __shared__ int tok[MOE_BM];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  int e, first, n_rows;
+  if (!moe_find_tile(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
+  const int tid = threadIdx.x, W = a.W, F = a.F;
+  const int f0 = blockIdx.y * MOE_BN;
+  if (tid < MOE_BM) tok[tid] = tid < n_rows ? a.perm[first + tid] / a.top : -1;
+  __syncthreads();
+  const T* wg = (const T*)a.w_gate + (size_t)e * F * W;
+  const T* wu = (const T*)a.w_up + (size_t)e * F * W;
+  const int tx = tid & 63, ty = tid >> 6;      // column, group of four rows
+  float accg[4] = {0.f, 0.f, 0.f, 0.f}, accu[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < W; k0 += MOE_BK) {
+    for (int i = tid; i < MOE_BM * MOE_BK; i += 256) {
+      const int r = i / MOE_BK, k = i % MOE_BK;
+      As[r][k] = (tok[r] >= 0 && k0 + k < W) ? to_f32<T>(((const T*)a.x)[(size_t)tok[r] * W + k0 + k]) : 0.f;
+    }
+    for (int i = tid; i < MOE_BN * MOE_BK; i += 256) {
+      const int n = i / MOE_BK, k = i % MOE_BK;
+      const bool ok = f0 + n < F && k0 + k < W;
+      Gs[n][k] = ok ? to_f32<T>(wg[(size_t)(f0 + n) * W + k0 + k]) : 0.f;
+      Us[n][k] = ok ? to_f32<T>(wu[(size_t)(f0 + n) * W + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_BK; ++k) {
+      const float g = Gs[tx][k], u = Us[tx][k];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float x = As[ty * 4 + r][k];
+        accg[r] = fmaf(x, g, accg[r]);
+        accu[r] = fmaf(x, u, accu[r]);
+      }
+    }
+    __syncthreads();
+  }
+  pdl_launch_dependents_if_large();
+  if (f0 + tx >= F) return;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = ty * 4 + r;
+    if (row >= n_rows) continue;
+    float g = accg[r], u = accu[r];
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    const float y = g / (1.0f + expf(-a.slope * g)) * (u + 1.0f);
+    ((T*)a.act)[(size_t)(first + row) * F + f0 + tx] = from_f32<T>(y);
+  }
+}
+
+// out[j, t, :] = s * (act[p] . Wd_e^T) for the pairs p = t * top + j of a tile
+template <typename T>
+__global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
+  __shared__ float As[MOE_BM][MOE_BK];
+  __shared__ float Bs[MOE_BN][MOE_BK + 1];
+  __shared__ int pair[MOE_BM];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  int e, first, n_rows;
+  if (!moe_find_tile(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
+  const int tid = threadIdx.x, W = a.W, F = a.F;
+  const int n0 = blockIdx.y * MOE_BN;
+  if (tid < MOE_BM) pair[tid] = tid < n_rows ? a.perm[first + tid] : -1;
+  __syncthreads();
+  const T* wd = (const T*)a.w_down + (size_t)e * W * F;
+  const int tx = tid & 63, ty = tid >> 6;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < F; k0 += MOE_BK) {
+    for (int i = tid; i < MOE_BM * MOE_BK; i += 256) {
+      const int r = i / MOE_BK, k = i % MOE_BK;
+      As[r][k] = (r < n_rows && k0 + k < F) ? to_f32<T>(((const T*)a.act)[(size_t)(first + r) * F + k0 + k]) : 0.f;
+    }
+    for (int i = tid; i < MOE_BN * MOE_BK; i += 256) {
+      const int n = i / MOE_BK, k = i % MOE_BK;
+      Bs[n][k] = (n0 + n < W && k0 + k < F) ? to_f32<T>(wd[(size_t)(n0 + n) * F + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_BK; ++k) {
+      const float b = Bs[tx][k];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[r] = fmaf(As[ty * 4 + r][k], b, acc[r]);
+    }
+    __syncthreads();
+  }
+  pdl_launch_dependents_if_large();
+  if (n0 + tx >= W) return;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = ty * 4 + r;
+    if (row >= n_rows) continue;
+    const int p = pair[row], t = p / a.top, j = p % a.top;
+    a.out[((size_t)j * a.T + t) * W + n0 + tx] = a.wts[p] * acc[r];
+  }
+}
+
+static int moe_check(const MoeArgs& a) {
+  if (a.T < 0 || a.W <= 0 || a.F <= 0 || a.E <= 0 || a.n_identity < 0 || a.top <= 0 ||
+      a.n_groups <= 0 || a.keep_groups <= 0 || a.keep_groups > a.n_groups)
+    return GB_ERR_BAD_ARG;
+  const int n_all = a.E + a.n_identity;
+  if (n_all % a.n_groups || a.top > n_all) return GB_ERR_BAD_ARG;
+  if (n_all > MOE_MAX_OUTPUTS) return GB_ERR_UNSUPPORTED;
+  if (!a.x || !a.router_w || !a.correction || !a.w_gate || !a.w_up || !a.w_down || !a.ids || !a.wts ||
+      !a.rank || !a.counts || !a.offsets || !a.perm || !a.act || !a.out)
+    return GB_ERR_BAD_ARG;
+  return 0;
+}
+
+template <typename T>
+static int moe_forward(const MoeArgs& a, cudaStream_t s) {
+  int e = moe_check(a);
+  if (e) return e;
+  if (a.T == 0) return 0;
+  const int n_all = a.E + a.n_identity;
+  e = gb_launch(moe_route_kernel<T>, dim3(a.T), dim3(128), (size_t)2 * n_all * sizeof(float), s, a);
+  if (e) return e;
+  e = gb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, a);
+  if (e) return e;
+  // the most tiles the pairs can make: every expert may end in a tile that is not full
+  const long long pairs = (long long)a.T * a.top;
+  const long long tiles = pairs / MOE_BM + (pairs < a.E ? pairs : a.E);
+  if (tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;
+  e = gb_launch(moe_up_kernel<T>, dim3((unsigned)tiles, (a.F + MOE_BN - 1) / MOE_BN), dim3(256), 0, s, a);
+  if (e) return e;
+  return gb_launch(moe_down_kernel<T>, dim3((unsigned)tiles, (a.W + MOE_BN - 1) / MOE_BN), dim3(256), 0, s, a);
+}
+
+// Four launches: route, sort, the experts' first products with their activation,
+// their second products with the weights.
+GB_EXPORT int gb_moe_forward_f32(const MoeArgs* a, cudaStream_t s) { return moe_forward<float>(*a, s); }
+GB_EXPORT int gb_moe_forward_bf16(const MoeArgs* a, cudaStream_t s) { return moe_forward<bf16>(*a, s); }

@@ -310,3 +310,104 @@ GB_EXPORT int gb_add_rmsnorm_bf16(const float* res_in, const void* delta, const 
   return launch<bf16, bf16>(res_in, delta, parts, n_parts, part_stride, rows, w, eps, res_out, y,
                             n_rows, N, s);
 }
+
+// ---- a contribution that passes through an RMS norm of its own ------------------
+//
+//   d   = delta[s, :]  (or the sum of n_parts 32-bit partial sums of it)
+//   c   = post_w ? d / sqrt(mean(d^2) + post_eps) * post_w : d
+//   c   = scale ? c * scale : c                      (a learned factor per channel)
+//   v   = res_in[s, :] + c                           (either may be absent; 32-bit)
+//   res_out[r, :] = v                                (optional)
+//   y[r, :] = w ? v / sqrt(mean(v^2) + eps) * w : v  (rounded to the activation type)
+//
+// for layers that normalise a sublayer's output instead of its input: the
+// sublayer that follows reads y = the stream itself.  All vectors are 32-bit.
+// One block per row keeps the row in shared memory between its passes; the
+// block's size, and with it the tree of its sums, depends on N only.
+struct PostNormArgs {
+  const float* res_in;
+  const void* delta;
+  const float* parts;
+  int n_parts;
+  long long part_stride;
+  const int* rows;
+  const float* post_w;
+  float post_eps;
+  const float* scale;
+  const float* w;
+  float eps;
+  float* res_out;
+  void* y;
+  int n_rows, N;
+};
+
+template <typename T>
+__global__ void add_postnorm_kernel(const PostNormArgs a) {
+  extern __shared__ float row[];   // [N]
+  __shared__ float scratch[32];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int N = a.N, r = blockIdx.x;
+  const size_t s = a.rows ? (size_t)a.rows[r] : (size_t)r;
+  const T* din = a.delta ? (const T*)a.delta + s * N : nullptr;
+  const float* pin = a.parts ? a.parts + s * N : nullptr;
+  const float* rin = a.res_in ? a.res_in + s * N : nullptr;
+  const bool has_d = din || pin;
+  float ss = 0.f;
+  if (has_d) {
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+      float d = din ? to_f32<T>(din[i]) : 0.f;
+      for (int k = 0; k < a.n_parts; ++k) d += pin[(size_t)k * a.part_stride + i];
+      row[i] = d;
+      ss += d * d;
+    }
+  }
+  float inv_d = 1.f;
+  if (has_d && a.post_w) inv_d = 1.0f / sqrtf(block_sum(ss, scratch) / (float)N + a.post_eps);
+  float* rout = a.res_out ? a.res_out + (size_t)r * N : nullptr;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < N; i += blockDim.x) {
+    float v = rin ? rin[i] : 0.f;
+    if (has_d) {
+      float c = row[i];
+      if (a.post_w) c = c * inv_d * a.post_w[i];
+      if (a.scale) c *= a.scale[i];
+      v += c;
+    }
+    if (rout) rout[i] = v;
+    row[i] = v;
+    ss += v * v;
+  }
+  pdl_launch_dependents_if_large();
+  T* yo = (T*)a.y + (size_t)r * N;
+  if (a.w) {
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)N + a.eps);
+    for (int i = threadIdx.x; i < N; i += blockDim.x) yo[i] = from_f32<T>(row[i] * inv * a.w[i]);
+  } else {
+    for (int i = threadIdx.x; i < N; i += blockDim.x) yo[i] = from_f32<T>(row[i]);
+  }
+}
+
+template <typename T>
+static int add_postnorm_launch(const PostNormArgs& a, cudaStream_t stream) {
+  if (a.n_rows < 0 || a.N <= 0 || !a.y || (!a.res_in && !a.delta && !a.parts)) return GB_ERR_BAD_ARG;
+  if (a.parts && a.n_parts <= 0) return GB_ERR_BAD_ARG;
+  if (a.n_rows == 0) return 0;
+  const size_t smem = (size_t)a.N * sizeof(float);
+  if (smem > 200 * 1024) return GB_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_postnorm_kernel<T>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int threads = ((a.N + 3) / 4 + 31) / 32 * 32;   // by N only
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  return gb_launch(add_postnorm_kernel<T>, dim3(a.n_rows), dim3(threads), smem, stream, a);
+}
+
+GB_EXPORT int gb_add_postnorm_f32(const PostNormArgs* a, cudaStream_t s) {
+  return add_postnorm_launch<float>(*a, s);
+}
+GB_EXPORT int gb_add_postnorm_bf16(const PostNormArgs* a, cudaStream_t s) {
+  return add_postnorm_launch<bf16>(*a, s);
+}

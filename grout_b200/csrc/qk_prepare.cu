@@ -27,7 +27,17 @@ struct QkPrepareArgs {
   int n_parts;              //   (the split-K projection leaves its reduction to this kernel)
   long long part_stride;    //   floats between partials
   int v_from_k;             // the projection has no v: a value is its key before the rotation
+  int Dv;                   // size of a value head in the projection (0: D)
+  int Ds;                   // width of a row of q_out, kv_out and the pages (0: D); the rest is zeros
+  float q_temp_coef;        // with q_temp_every > 0 a query at position p is multiplied, after its
+  int q_temp_every;         //   norm, by 1 + coef * ln(floor((p + 1) / every) + 1)
 };
+
+__device__ __forceinline__ float query_temperature(const QkPrepareArgs& a, int pos) {
+  return a.q_temp_every > 0
+             ? 1.0f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every + 1))
+             : 1.0f;
+}
 
 template <typename T, typename WT>
 __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
@@ -39,44 +49,60 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
   if (head >= n_heads) return;  // warps are independent below
-  const int D = a.D;
-  float* x = sm + warp * D;
-  const T* src = (const T*)a.qkv + ((size_t)t * n_heads + head) * D;
+  const int Dv = a.Dv > 0 ? a.Dv : a.D;     // a value head's size in the projection
+  const int Ds = a.Ds > 0 ? a.Ds : a.D;     // a stored row's width
   const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+  const int D = kind == 2 ? Dv : a.D;
+  const int wider = a.D > Dv ? a.D : Dv;
+  float* x = sm + warp * (wider > Ds ? wider : Ds);
+  // columns of the projection: q heads, k heads (both of a.D), then v heads of Dv
+  const size_t width = (size_t)(a.nq + a.nkv) * a.D + (a.v_from_k ? 0 : (size_t)a.nkv * Dv);
+  const size_t col0 = kind == 2 ? (size_t)(a.nq + a.nkv) * a.D + (size_t)(head - a.nq - a.nkv) * Dv
+                                : (size_t)head * a.D;
   if (a.qkv_parts) {
-    const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
+    const float* ps = a.qkv_parts + (size_t)t * width + col0;
     for (int d = lane; d < D; d += 32) {
       float v = 0.f;
       for (int k = 0; k < a.n_parts; ++k) v += ps[(size_t)k * a.part_stride + d];
       x[d] = v;
     }
   } else {
+    const T* src = (const T*)a.qkv + (size_t)t * width + col0;
     for (int d = lane; d < D; d += 32) x[d] = to_f32<T>(src[d]);
   }
+  for (int d = D + lane; d < Ds; d += 32) x[d] = 0.f;   // a narrower head is filled up with zeros
   __syncwarp();
   pdl_launch_dependents_if_large();
+  const int pos = a.token_pos[t];
   const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
   if (w) {
     float ss = 0.f;
     for (int d = lane; d < D; d += 32) ss += x[d] * x[d];
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
-    for (int d = lane; d < D; d += 32) x[d] = x[d] * inv * to_f32<WT>(w[d]);
+    const float temp = kind == 0 ? query_temperature(a, pos) : 1.0f;
+    for (int d = lane; d < D; d += 32) {
+      const float v = x[d] * inv * to_f32<WT>(w[d]);
+      x[d] = a.q_temp_every > 0 && kind == 0 ? v * temp : v;
+    }
+    __syncwarp();
+  } else if (kind == 0 && a.q_temp_every > 0) {
+    const float temp = query_temperature(a, pos);
+    for (int d = lane; d < D; d += 32) x[d] *= temp;
     __syncwarp();
   }
-  const int pos = a.token_pos[t];
   if (kind == 1 && a.v_from_k) {   // the value: the key as it stands now
     const int hh = head - a.nq;
     if (a.kv_out) {
-      T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + a.nkv + hh) * D;
-      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+      T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + a.nkv + hh) * Ds;
+      for (int d = lane; d < Ds; d += 32) dst[d] = from_f32<T>(x[d]);
     }
     if (a.k_pages) {
       const int slot = a.slots[a.token_seq[t]];
       if (slot >= 0) {
         T* dst = (T*)a.v_pages +
-                 paged_row(a.block_table + (size_t)slot * a.max_pages, pos, hh, a.nkv, a.page, D);
-        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+                 paged_row(a.block_table + (size_t)slot * a.max_pages, pos, hh, a.nkv, a.page, Ds);
+        for (int d = lane; d < Ds; d += 32) dst[d] = from_f32<T>(x[d]);
       }
     }
   }
@@ -93,22 +119,22 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
     __syncwarp();
   }
   if (kind == 0) {
-    T* dst = (T*)a.q_out + ((size_t)t * a.nq + head) * D;
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+    T* dst = (T*)a.q_out + ((size_t)t * a.nq + head) * Ds;
+    for (int d = lane; d < Ds; d += 32) dst[d] = from_f32<T>(x[d]);
     return;
   }
   const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
   if (a.kv_out) {
-    T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+    T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * Ds;
+    for (int d = lane; d < Ds; d += 32) dst[d] = from_f32<T>(x[d]);
   }
   if (a.k_pages) {
     const int slot = a.slots[a.token_seq[t]];
     if (slot < 0) return;  // padding row: nothing is stored
     const int* table = a.block_table + (size_t)slot * a.max_pages;
     T* base = (T*)(kind == 1 ? a.k_pages : a.v_pages);
-    T* dst = base + paged_row(table, pos, hh, a.nkv, a.page, D);
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+    T* dst = base + paged_row(table, pos, hh, a.nkv, a.page, Ds);
+    for (int d = lane; d < Ds; d += 32) dst[d] = from_f32<T>(x[d]);
   }
 }
 
@@ -601,7 +627,10 @@ static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
   const int n_heads = a.nq + (a.v_from_k ? 1 : 2) * a.nkv;
   dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
-  const size_t smem = (size_t)warps * a.D * sizeof(float);
+  int widest = a.D;
+  if (a.Dv > widest) widest = a.Dv;
+  if (a.Ds > widest) widest = a.Ds;
+  const size_t smem = (size_t)warps * widest * sizeof(float);
   if (smem > 48 * 1024) return GB_ERR_UNSUPPORTED;
   return gb_launch(qk_prepare_kernel<T, WT>, grid, dim3(warps * 32), smem, stream, a);
 }
@@ -617,7 +646,16 @@ static int check(const QkPrepareArgs& a) {
     return GB_ERR_BAD_ARG;
   if (!a.token_pos) return GB_ERR_BAD_ARG;
   if (a.v_from_k && (a.k_w || a.nkv <= 0)) return GB_ERR_UNSUPPORTED;
+  if (a.Dv < 0 || a.Ds < 0 || (a.Ds > 0 && (a.Ds < a.D || a.Ds < a.Dv))) return GB_ERR_BAD_ARG;
+  if (a.q_temp_every < 0) return GB_ERR_BAD_ARG;
   return 0;
+}
+
+// The kernels that keep a head in registers know one head size and no query
+// temperature; heads of two sizes, filled-up rows and the temperature take the
+// plain kernel.
+static bool plain_only(const QkPrepareArgs& a) {
+  return (a.Dv > 0 && a.Dv != a.D) || (a.Ds > 0 && a.Ds != a.D) || a.q_temp_every > 0;
 }
 
 GB_EXPORT int gb_qk_prepare_f32(const QkPrepareArgs* a, int w_is_f32, cudaStream_t s) {
@@ -631,6 +669,7 @@ GB_EXPORT int gb_qk_prepare_bf16(const QkPrepareArgs* a, int w_is_f32, cudaStrea
   int e = check(*a);
   if (e) return e;
   if (a->n_tokens == 0) return 0;
+  if (plain_only(*a)) return w_is_f32 ? launch<bf16, float>(*a, s) : launch<bf16, bf16>(*a, s);
   if (fast_ok(*a) && wide_ok(*a)) return w_is_f32 ? launch_wide<float>(*a, s) : launch_wide<bf16>(*a, s);
   if (fast_ok(*a)) return w_is_f32 ? launch_fast<float>(*a, s) : launch_fast<bf16>(*a, s);
   if (chunk_ok(*a)) return w_is_f32 ? launch_chunk<float>(*a, s) : launch_chunk<bf16>(*a, s);

@@ -102,6 +102,8 @@ class Model:
         layout = self.cache_layout()
         pending = self.embedding.forward(step.tokens, step)
         res = None
+        if self.embedding.starts_stream:      # the embedding is the 32-bit stream already
+            res, pending = pending, None
         for i, e in enumerate(self.plan.schedule):
             owner = i if e.cache_of is None else e.cache_of
             view = cache.view(owner) if owner in layout.where else None

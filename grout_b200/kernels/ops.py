@@ -245,6 +245,27 @@ def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_profiled("embed_pos_norm", lambda out, table, positions, ids, pos, w, eps: (_nbytes(ids, pos, out) + out.numel() * 2 * table.element_size(), 0))
+def embed_pos_norm(table: torch.Tensor, positions: torch.Tensor, ids: torch.Tensor,
+                   token_pos: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """rmsnorm(table[ids[t]] + positions[token_pos[t]]) * weight as 32-bit rows [T, H]: the
+    sum and the norm are 32-bit whatever the tables' type."""
+    _need(table, "embedding table", ndim=2)
+    _need(positions, "position table", table.dtype, 2)
+    _need(ids, "token ids", torch.int32, 1)
+    _need(token_pos, "token positions", torch.int32, 1)
+    _need(weight, "norm weight", torch.float32, 1)
+    V, H = table.shape
+    if positions.shape[1] != H or weight.shape[0] != H or token_pos.shape[0] != ids.shape[0]:
+        raise KernelError("the tables, the norm weight and the position list do not fit together")
+    out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    _check(_fn("embed", f"gb_embed_pos_norm_{_suffix(table.dtype)}", "pppppfpiiiip")(
+        table.data_ptr(), positions.data_ptr(), ids.data_ptr(), token_pos.data_ptr(),
+        weight.data_ptr(), float(eps), out.data_ptr(), ids.shape[0], H, V, positions.shape[0],
+        _stream()), "embed_pos_norm")
+    return out
+
+
 # ---------------------------------------------------------------- norm
 @_profiled("add_rmsnorm", _cost_io)
 def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
@@ -370,6 +391,66 @@ def add_layernorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
     return res_out, y
 
 
+class _PostNormArgs(ctypes.Structure):
+    _fields_ = [("res_in", _P), ("delta", _P), ("parts", _P), ("n_parts", _I), ("part_stride", _L),
+                ("rows", _P), ("post_w", _P), ("post_eps", _F), ("scale", _P), ("w", _P),
+                ("eps", _F), ("res_out", _P), ("y", _P), ("n_rows", _I), ("N", _I)]
+
+
+@_profiled("add_postnorm", _cost_io)
+def add_postnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor], *,
+                 dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                 post_weight: Optional[torch.Tensor] = None, post_eps: float = 0.0,
+                 scale: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                 eps: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """v = res_in + scale * rmsnorm(delta; post_weight, post_eps) in 32-bit -> (v, y), where
+    y = rmsnorm(v; weight, eps) or, without ``weight``, v itself, in ``dtype``.  Without
+    ``post_weight`` delta is added as it is, without ``scale`` unscaled.  ``delta`` is [T, N]
+    in ``dtype`` or a stack of 32-bit partial sums [S, T, N], added in order; all vectors
+    are 32-bit [N].  Without ``rows`` the stream is updated in place when given."""
+    parts = None
+    if delta is not None and delta.dim() == 3:
+        _need(delta, "partial sums", torch.float32, 3)
+        parts, delta = delta, None
+    src = res_in if res_in is not None else (delta if delta is not None else
+                                             (parts[0] if parts is not None else None))
+    if src is None:
+        raise KernelError("add_postnorm needs a residual or a delta")
+    if res_in is not None:
+        _need(res_in, "residual", torch.float32, 2)
+    if delta is not None:
+        _need(delta, "delta", dtype, 2)
+    for t in (delta, parts[0] if parts is not None else None):
+        if t is not None and res_in is not None and tuple(t.shape) != tuple(res_in.shape):
+            raise KernelError(f"residual {tuple(res_in.shape)} and delta {tuple(t.shape)} differ")
+    N = src.shape[1]
+    for t, nm in ((post_weight, "inner norm weight"), (scale, "scale"), (weight, "norm weight")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.shape[0] != N:
+                raise KernelError(f"{nm} has {t.shape[0]} elements for rows of {N}")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+    n_rows = rows.shape[0] if rows is not None else src.shape[0]
+    nothing_added = delta is None and parts is None
+    if nothing_added and rows is None and weight is None and dtype == torch.float32:
+        return res_in, res_in                       # the stream is its own 32-bit reading
+    if rows is None and res_in is not None:
+        res_out = None if nothing_added else res_in
+    else:
+        res_out = torch.empty((n_rows, N), dtype=torch.float32, device=src.device)
+    y = torch.empty((n_rows, N), dtype=dtype, device=src.device)
+    a = _PostNormArgs()
+    a.res_in, a.delta, a.parts = _ptr(res_in), _ptr(delta), _ptr(parts)
+    a.n_parts = 0 if parts is None else parts.shape[0]
+    a.part_stride = 0 if parts is None else parts.stride(0)
+    a.rows, a.post_w, a.post_eps, a.scale = _ptr(rows), _ptr(post_weight), float(post_eps), _ptr(scale)
+    a.w, a.eps, a.res_out, a.y, a.n_rows, a.N = _ptr(weight), float(eps), _ptr(res_out), y.data_ptr(), n_rows, N
+    _check(_fn("norm", f"gb_add_postnorm_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "add_postnorm")
+    return (res_in if res_out is None else res_out), y
+
+
 # ---------------------------------------------------------------- q/k preparation
 class _QkPrepareArgs(ctypes.Structure):
     _fields_ = [("qkv", _P), ("q_w", _P), ("k_w", _P), ("inv_freq", _P), ("token_seq", _P),
@@ -377,18 +458,25 @@ class _QkPrepareArgs(ctypes.Structure):
                 ("kv_out", _P), ("k_pages", _P), ("v_pages", _P), ("eps", _F),
                 ("n_tokens", _I), ("nq", _I), ("nkv", _I), ("D", _I), ("rot_dim", _I),
                 ("max_pages", _I), ("page", _I), ("qkv_parts", _P), ("n_parts", _I),
-                ("part_stride", _L), ("v_from_k", _I)]
+                ("part_stride", _L), ("v_from_k", _I), ("Dv", _I), ("Ds", _I),
+                ("q_temp_coef", _F), ("q_temp_every", _I)]
 
 
 @_profiled("qk_prepare", lambda out, qkv, nq, nkv, D, **k: _cost_qk_prepare(out, qkv, nq, nkv, D))
 def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=None,
                eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
                block_table=None, k_pages=None, v_pages=None, page: int = 0,
-               want_kv_out: bool = False, values_are_keys: bool = False):
-    """Returns (q [T, nq, D], kv_out or None); writes k, v into the pages when given.
+               want_kv_out: bool = False, values_are_keys: bool = False,
+               v_dim: Optional[int] = None, q_temp: Optional[Tuple[float, int]] = None):
+    """Returns (q [T, nq, Ds], kv_out or None); writes k, v into the pages when given.
     ``qkv`` may be a stack of 32-bit partial sums [S, T, width] of the projection
     (bf16 engines only): they are added in order.  ``values_are_keys``: the
-    projection holds q and k only, and a value is its key before the rotation."""
+    projection holds q and k only, and a value is its key before the rotation.
+    ``v_dim``: the size of a value head in the projection when it is not D; the
+    rows that are written (q, kv_out, pages) are then Ds wide, Ds being the pages'
+    row width (at least D and ``v_dim``) or, without pages, the larger of the two,
+    and end in zeros.  ``q_temp`` = (coef, every): a query at position p is
+    multiplied, after its norm, by 1 + coef * ln(floor((p + 1) / every) + 1)."""
     parts = None
     if qkv.dim() == 3:
         _need(qkv, "qkv partial sums", torch.float32, 3)
@@ -399,10 +487,16 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
         _need(qkv, "qkv", ndim=2)
         dt = qkv.dtype
     T = qkv.shape[-2]
-    n_in = nq + (nkv if values_are_keys else 2 * nkv)
-    if qkv.shape[-1] != n_in * D:
-        raise KernelError(f"the projection has {qkv.shape[-1]} columns, expected {n_in} heads of "
-                          f"{D} = {n_in * D}")
+    Dv = int(v_dim) if v_dim else D
+    if Dv != D and (values_are_keys or nkv == 0):
+        raise KernelError("values of another size than the keys need a v projection")
+    Ds = int(k_pages.shape[-1]) if k_pages is not None else max(D, Dv)
+    if Ds < max(D, Dv):
+        raise KernelError(f"pages with rows of {Ds} cannot hold heads of {D} and {Dv}")
+    width = (nq + nkv) * D + (0 if values_are_keys else nkv * Dv)
+    if qkv.shape[-1] != width:
+        raise KernelError(f"the projection has {qkv.shape[-1]} columns, expected {nq} + {nkv} heads of "
+                          f"{D}" + ("" if values_are_keys else f" and {nkv} of {Dv}") + f" = {width}")
     w_is_f32 = int(dt == torch.float32)      # without norm weights: whatever the entry point takes
     for w, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
         if w is not None:
@@ -419,8 +513,8 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     _need(token_pos, "token_pos", torch.int32, 1)
     _need(token_seq, "token_seq", torch.int32, 1)
     _need(slots, "slots", torch.int32, 1)
-    q = torch.empty((T, nq, D), dtype=dt, device=qkv.device)
-    kv_out = torch.empty((T, 2 * nkv, D), dtype=dt, device=qkv.device) if want_kv_out else None
+    q = torch.empty((T, nq, Ds), dtype=dt, device=qkv.device)
+    kv_out = torch.empty((T, 2 * nkv, Ds), dtype=dt, device=qkv.device) if want_kv_out else None
     a = _QkPrepareArgs()
     a.qkv, a.q_w, a.k_w, a.inv_freq = (None if parts is not None else qkv.data_ptr()), _ptr(q_w), \
         _ptr(k_w), _ptr(inv_freq)
@@ -430,12 +524,15 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     a.q_out, a.kv_out = q.data_ptr(), _ptr(kv_out)
     a.eps, a.n_tokens, a.nq, a.nkv, a.D, a.rot_dim = float(eps), T, nq, nkv, D, int(rot_dim)
     a.v_from_k = int(values_are_keys)
+    a.Dv, a.Ds = Dv, Ds
+    if q_temp:
+        a.q_temp_coef, a.q_temp_every = float(q_temp[0]), int(q_temp[1])
     if k_pages is not None:
         _need(k_pages, "k pages", dt, 4)
         _need(v_pages, "v pages", dt, 4)
         _need(block_table, "block table", torch.int32, 2)
-        if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
-            raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, {nkv}, {page}, {D}]")
+        if tuple(k_pages.shape[1:]) != (nkv, page, Ds) or v_pages.shape != k_pages.shape:
+            raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, {nkv}, {page}, {Ds}]")
         a.block_table, a.k_pages, a.v_pages = block_table.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr()
         a.max_pages, a.page = block_table.shape[1], page
     sfx = _suffix(dt)
@@ -530,6 +627,20 @@ def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     sfx = _suffix(gate_up.dtype)
     _check(_fn("elementwise", f"gb_silu_mul_{sfx}", "ppiiip")(
         gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "silu_mul")
+    return out
+
+
+@_profiled("gelu_tanh_mul", _cost_io)
+def gelu_tanh_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """gelu_tanh(gate) * up, gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)));
+    the layout of ``gate_up`` is that of ``silu_mul``."""
+    _need(gate_up, "gate|up", ndim=2)
+    T, two_i = gate_up.shape
+    if two_i % 2 or (interleave and two_i % (2 * interleave)):
+        raise KernelError("gate|up must have an even number of columns (of whole groups)")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_fn("elementwise", f"gb_gelu_tanh_mul_{_suffix(gate_up.dtype)}", "ppiiip")(
+        gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "gelu_tanh_mul")
     return out
 
 
@@ -1228,6 +1339,138 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
                         window=window, softcap=softcap, sinks=sinks)
+
+
+# ---------------------------------------------------------------- gated delta rule
+class _DeltaArgs(ctypes.Structure):
+    _fields_ = [("proj", _P), ("conv_w", _P), ("a_log", _P), ("dt_bias", _P), ("norm_w", _P),
+                ("token_seq", _P), ("cu_q", _P), ("slots", _P), ("state", _P), ("state_stride", _L),
+                ("prep", _P), ("o", _P), ("y", _P), ("n_tokens", _I), ("n_seqs", _I), ("H", _I),
+                ("G", _I), ("dk", _I), ("dv", _I), ("taps", _I), ("unit_eps", _F), ("norm_eps", _F)]
+
+
+def delta_state_floats(H: int, G: int, dk: int, dv: int, taps: int) -> int:
+    """Floats of one sequence's state: the convolutions' tail, then the heads' matrices."""
+    return (taps - 1) * (2 * G * dk + H * dv) + H * dv * dk
+
+
+def _cost_delta(out, proj, state, *a, H, G, dk, dv, taps, **k):
+    T = proj.shape[0]
+    n_seqs = k["slots"].shape[0]
+    return (_nbytes(proj, out) + 2 * T * (2 * G * dk + 2 * H * dv + 2 * H) * 4 +
+            2 * n_seqs * H * dk * dv * 4, 6.0 * T * H * dk * dv)
+
+
+@_profiled("delta_forward", _cost_delta)
+def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
+                  a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, *, H: int,
+                  G: int, dk: int, dv: int, taps: int, unit_eps: float, norm_eps: float,
+                  token_seq, cu_q, slots, dtype: torch.dtype) -> torch.Tensor:
+    """The gated delta rule on the rows of a step.  ``proj`` [T, C] 32-bit: the columns
+    q [G dk] | k [G dk] | v [H dv] | gate [H dv] | b [H] | a [H] of the mixer's one
+    projection; ``state`` [slots, delta_state_floats] 32-bit, updated in place for the
+    sequences whose slot is not negative; ``conv_w`` [2 G dk + H dv, taps].  Returns
+    y [T, H dv] in ``dtype``: every head's read-out, normalised over dv, times ``norm_w``
+    and silu(gate)."""
+    _need(proj, "projection", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    Cc = 2 * G * dk + H * dv
+    T = proj.shape[0]
+    if proj.shape[1] != Cc + H * dv + 2 * H:
+        raise KernelError(f"the projection has {proj.shape[1]} columns, expected {Cc + H * dv + 2 * H}")
+    if state.shape[1] != delta_state_floats(H, G, dk, dv, taps):
+        raise KernelError(f"a sequence's state has {state.shape[1]} floats, expected "
+                          f"{delta_state_floats(H, G, dk, dv, taps)}")
+    for t, nm, shape in ((conv_w, "convolution weights", (Cc, taps)), (a_log, "A_log", (H,)),
+                         (dt_bias, "dt_bias", (H,)), (norm_w, "norm weight", (dv,))):
+        _need(t, nm, torch.float32)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"{nm} are {tuple(t.shape)}, expected {shape}")
+    for t, nm in ((token_seq, "token_seq"), (cu_q, "cu_q"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    n_seqs = slots.shape[0]
+    if token_seq.shape[0] != T or cu_q.shape[0] != n_seqs + 1:
+        raise KernelError("token_seq, cu_q and slots do not describe the step's rows")
+    prep = torch.empty((T, Cc + 2 * H), dtype=torch.float32, device=proj.device)
+    o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
+    y = torch.empty((T, H * dv), dtype=dtype, device=proj.device)
+    a = _DeltaArgs()
+    a.proj, a.conv_w, a.a_log, a.dt_bias, a.norm_w = (proj.data_ptr(), conv_w.data_ptr(),
+                                                      a_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr())
+    a.token_seq, a.cu_q, a.slots = token_seq.data_ptr(), cu_q.data_ptr(), slots.data_ptr()
+    a.state, a.state_stride = state.data_ptr(), state.stride(0)
+    a.prep, a.o, a.y = prep.data_ptr(), o.data_ptr(), y.data_ptr()
+    a.n_tokens, a.n_seqs, a.H, a.G, a.dk, a.dv, a.taps = T, n_seqs, H, G, dk, dv, taps
+    a.unit_eps, a.norm_eps = float(unit_eps), float(norm_eps)
+    _check(_fn("delta", f"gb_delta_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "delta_forward", 4 if taps > 1 else 3)
+    return y
+
+
+# ---------------------------------------------------------------- routed experts
+class _MoeArgs(ctypes.Structure):
+    _fields_ = [("x", _P), ("router_w", _P), ("correction", _P), ("w_gate", _P), ("w_up", _P),
+                ("w_down", _P), ("ids", _P), ("wts", _P), ("rank", _P), ("counts", _P),
+                ("offsets", _P), ("perm", _P), ("act", _P), ("out", _P), ("T", _I), ("W", _I),
+                ("F", _I), ("E", _I), ("n_identity", _I), ("top", _I), ("n_groups", _I),
+                ("keep_groups", _I), ("limit", _F), ("slope", _F)]
+
+
+_MOE_COUNTS = {}
+
+
+def _cost_moe(out, x, router_w, correction, w_gate, w_up, w_down, *, top, **k):
+    T, W = x.shape
+    E, F = w_gate.shape[0], w_gate.shape[1]
+    used = min(E, T * top)
+    return (_nbytes(x, out) + used * 3 * F * W * w_gate.element_size(), 6.0 * T * top * F * W)
+
+
+@_profiled("moe_forward", _cost_moe)
+def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: torch.Tensor,
+                w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *, top: int,
+                n_identity: int, n_groups: int, keep_groups: int, limit: float, slope: float,
+                want_choice: bool = False):
+    """A feed-forward of routed experts on rows x [T, W] -> 32-bit partial sums
+    [top, T, W], choice j of every token in [j], already weighted; their sum is the
+    feed-forward's output.  ``router_w`` [E + n_identity, W] and ``correction`` are
+    32-bit; the experts' weights [E, F, W], [E, F, W], [E, W, F] have the type of x.
+    The last ``n_identity`` router outputs stand for experts that return their input.
+    With ``want_choice`` also returns (ids [T, top] int32, weights [T, top])."""
+    _need(x, "activations", ndim=2)
+    T, W = x.shape
+    _need(router_w, "router weight", torch.float32, 2)
+    _need(correction, "score correction", torch.float32, 1)
+    for t, nm in ((w_gate, "gate weights"), (w_up, "up weights"), (w_down, "down weights")):
+        _need(t, nm, x.dtype, 3)
+    E, F = w_gate.shape[0], w_gate.shape[1]
+    n_all = E + n_identity
+    if tuple(w_gate.shape) != (E, F, W) or tuple(w_up.shape) != (E, F, W) or \
+            tuple(w_down.shape) != (E, W, F) or tuple(router_w.shape) != (n_all, W) or \
+            correction.shape[0] != n_all:
+        raise KernelError("the experts' weights, the router and the correction do not fit together")
+    dev = x.device
+    ids = torch.empty((T, top), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, top), dtype=torch.float32, device=dev)
+    rank = torch.empty((T, top), dtype=torch.int32, device=dev)
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    perm = torch.empty((T * top,), dtype=torch.int32, device=dev)
+    act = torch.empty((T * top, F), dtype=x.dtype, device=dev)
+    out = torch.empty((top, T, W), dtype=torch.float32, device=dev)
+    key = (dev.index or 0, E)
+    counts = _MOE_COUNTS.get(key)      # zero between calls: the kernels leave it so
+    if counts is None:
+        counts = _MOE_COUNTS[key] = torch.zeros((E,), dtype=torch.int32, device=dev)
+    a = _MoeArgs()
+    a.x, a.router_w, a.correction = x.data_ptr(), router_w.data_ptr(), correction.data_ptr()
+    a.w_gate, a.w_up, a.w_down = w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr()
+    a.ids, a.wts, a.rank, a.counts = ids.data_ptr(), wts.data_ptr(), rank.data_ptr(), counts.data_ptr()
+    a.offsets, a.perm, a.act, a.out = offsets.data_ptr(), perm.data_ptr(), act.data_ptr(), out.data_ptr()
+    a.T, a.W, a.F, a.E, a.n_identity, a.top = T, W, F, E, int(n_identity), int(top)
+    a.n_groups, a.keep_groups, a.limit, a.slope = int(n_groups), int(keep_groups), float(limit), float(slope)
+    _check(_fn("moe", f"gb_moe_forward_{_suffix(x.dtype)}", "pp")(ctypes.addressof(a), _stream()),
+           "moe_forward", 4)
+    return (out, ids, wts) if want_choice else out
 
 
 # ---------------------------------------------------------------- sampling

@@ -14,8 +14,8 @@ from typing import Dict
 
 from typing import Optional
 
-from .base import BuildContext, Part, PartSpec, build_part, register_part
-from .norm import Contribution
+from .base import BuildContext, ParamSpec, Part, PartSpec, build_part, register_part
+from .norm import Contribution, stream_add
 
 
 class Block(Part):
@@ -107,3 +107,65 @@ class SandwichBlock(Block):
             return res, a
         res, m = self.norm2.add_norm(res, a)
         return res, Contribution(self.feedforward.forward(m, step), self.norm2b, self.mult)
+
+
+@register_part("block", "postnorm")
+class PostNormBlock(Block):
+    """A norm behind every sublayer and none in front of it: the sublayers read
+    the stream as it is, and what they return is normalised, multiplied channel
+    by channel by a learned vector ("layer scale") and added:
+
+        x += scale1 * norm1(mixer(x));  x += scale2 * norm2(feedforward(x))
+
+    The second line is absent when the layer has no feed-forward; a scale is
+    absent when its tensor's name is None.  ``scale1`` / ``scale2`` are the
+    tensors' names under the layer's prefix.  A sublayer's output leaves here as a
+    ``Contribution``, so each sublayer boundary is one kernel: normalise, scale,
+    add in 32-bit, round for the next reader."""
+
+    def __init__(self, ctx: BuildContext, mixer: PartSpec, norm1: PartSpec,
+                 scale1: Optional[str] = None, feedforward: Optional[PartSpec] = None,
+                 norm2: Optional[PartSpec] = None, scale2: Optional[str] = None):
+        super().__init__(ctx)
+        if (feedforward is None) != (norm2 is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is there")
+        self.mixer = build_part("mixer", mixer, ctx)
+        self.norm1 = build_part("norm", norm1, ctx)
+        self.feedforward = build_part("feedforward", feedforward, ctx) if feedforward else None
+        self.norm2 = build_part("norm", norm2, ctx) if norm2 else None
+        self.scale_names = (scale1, scale2 if feedforward else None)
+        self.scale1 = self.scale2 = None
+        self.width = self.norm1.dim
+
+    def named_parts(self) -> Dict[str, Part]:
+        roles = ("mixer", "norm1", "feedforward", "norm2")
+        return {r: getattr(self, r) for r in roles if getattr(self, r) is not None}
+
+    def children(self):
+        return tuple(self.named_parts().values())
+
+    def param_specs(self):
+        return {n: ParamSpec((self.width,), "vector") for n in self.scale_names if n}
+
+    def load(self, params):
+        # 32-bit whatever the checkpoint stores: the sum into the stream is 32-bit
+        s1, s2 = self.scale_names
+        self.scale1 = params[s1].float().contiguous() if s1 else None
+        self.scale2 = params[s2].float().contiguous() if s2 else None
+
+    def kernel_modules(self):
+        return ("norm",)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, res, pending, step, cache):
+        res, x = stream_add(res, pending, self.ctx.dtype)
+        a = Contribution(self.mixer.forward(x, step, cache), self.norm1, scale=self.scale1)
+        if self.feedforward is None:
+            return res, a
+        res, x = stream_add(res, a, self.ctx.dtype)
+        return res, Contribution(self.feedforward.forward(x, step), self.norm2, scale=self.scale2)

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import ops
 from .base import BuildContext, ParamSpec, Part, register_part
 from .linear import Linear
 
@@ -90,3 +91,111 @@ class ReluSquaredMLP(FeedForward):
 
     def forward(self, x, step):
         return self.down(self.up.relu_squared(x), partial_ok=True)
+
+
+@register_part("feedforward", "gated_mlp")
+class GatedMLP(FeedForward):
+    """d = (act(x Wg^T) * (x Wu^T)) Wd^T, no biases, with ``activation`` "silu" or
+    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  Gate and up are
+    one product; the activation and the multiplication are taken in 32-bit on its
+    result.  ``names``: the local names of the three tensors (keys gate, up, down)."""
+
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, ctx: BuildContext, hidden: int, intermediate: int,
+                 activation: str = "silu", names=None):
+        super().__init__(ctx)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}': one of {list(self.ACTIVATIONS)}")
+        self.hidden, self.intermediate, self.activation = int(hidden), int(intermediate), activation
+        self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight",
+                           "down": "down_proj.weight"}, **(names or {}))
+        self.gate_up = self.down = None
+
+    def param_specs(self):
+        nm = self.names
+        return {nm["gate"]: ParamSpec((self.intermediate, self.hidden)),
+                nm["up"]: ParamSpec((self.intermediate, self.hidden)),
+                nm["down"]: ParamSpec((self.hidden, self.intermediate))}
+
+    def load(self, params):
+        g, u = params[self.names["gate"]], params[self.names["up"]]
+        if g.dtype != u.dtype:
+            raise ValueError("gate and up projections must be stored in one dtype to be fused")
+        self.gate_up = Linear(torch.cat([g, u], dim=0), self.ctx.products)
+        self.down = Linear(params[self.names["down"]], self.ctx.products)
+
+    def kernel_modules(self):
+        return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step):
+        gu = self.gate_up(x)
+        h = ops.silu_mul(gu, 0) if self.activation == "silu" else ops.gelu_tanh_mul(gu, 0)
+        return self.down(h, partial_ok=True)
+
+
+@register_part("feedforward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """``n_experts`` small gated feed-forwards of which every token uses ``top``.
+
+        z = Wr x (32-bit), s = softmax(z) over all n_experts + n_identity outputs
+        c = s + correction;  the outputs form ``n_groups`` equal groups of neighbours,
+        a group's score is its largest c, only outputs of the ``keep_groups`` best
+        groups can be chosen; the ``top`` largest c are chosen and weigh in with s
+        expert:  g = min(Wg x, limit), u = clamp(Wu x, -limit, limit),
+                 y = Wd (g sigmoid(gate_slope g) (u + 1))
+        the last ``n_identity`` outputs stand for experts that return x itself
+        out = sum of s * y over the chosen; the weights are not renormalised
+
+    Tensors: ``router`` [n_experts + n_identity, hidden], ``correction``, and per
+    expert j ``e<j>.gate`` / ``e<j>.up`` [intermediate, hidden], ``e<j>.down``.  The
+    result leaves as ``top`` weighted 32-bit partial sums, which the next norm adds."""
+
+    def __init__(self, ctx: BuildContext, hidden: int, intermediate: int, n_experts: int, top: int,
+                 limit: float, gate_slope: float, n_identity: int = 0, n_groups: int = 1,
+                 keep_groups: int = 1):
+        super().__init__(ctx)
+        self.hidden, self.intermediate = int(hidden), int(intermediate)
+        self.E, self.n_identity, self.top = int(n_experts), int(n_identity), int(top)
+        self.n_groups, self.keep_groups = int(n_groups), int(keep_groups)
+        self.limit, self.gate_slope = float(limit), float(gate_slope)
+        n_all = self.E + self.n_identity
+        if n_all % self.n_groups or not 1 <= self.keep_groups <= self.n_groups:
+            raise ValueError(f"{n_all} router outputs do not form {self.n_groups} equal groups "
+                             f"of which {self.keep_groups} are kept")
+        if not 1 <= self.top <= self.keep_groups * (n_all // self.n_groups):
+            raise ValueError(f"top={self.top} exceeds what {self.keep_groups} groups hold")
+        self.router_w = self.correction = self.w_gate = self.w_up = self.w_down = None
+
+    def param_specs(self):
+        n_all = self.E + self.n_identity
+        specs = {"router": ParamSpec((n_all, self.hidden)),
+                 "correction": ParamSpec((n_all,), "offset")}
+        for j in range(self.E):
+            specs[f"e{j}.gate"] = ParamSpec((self.intermediate, self.hidden))
+            specs[f"e{j}.up"] = ParamSpec((self.intermediate, self.hidden))
+            specs[f"e{j}.down"] = ParamSpec((self.hidden, self.intermediate))
+        return specs
+
+    def load(self, params):
+        # the router is 32-bit whatever the checkpoint stores
+        self.router_w = params["router"].float().contiguous()
+        self.correction = params["correction"].float().contiguous()
+        stack = lambda what: torch.stack([params[f"e{j}.{what}"] for j in range(self.E)]).to(
+            self.ctx.dtype).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+
+    def kernel_modules(self):
+        return ("moe",)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, x, step):
+        return ops.moe_forward(x, self.router_w, self.correction, self.w_gate, self.w_up,
+                               self.w_down, top=self.top, n_identity=self.n_identity,
+                               n_groups=self.n_groups, keep_groups=self.keep_groups,
+                               limit=self.limit, slope=self.gate_slope)

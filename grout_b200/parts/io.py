@@ -12,6 +12,9 @@ from .linear import Linear
 
 class Embedding(Part):
     family = "embedding"
+    #: True when ``forward`` returns the 32-bit residual stream itself instead of
+    #: a first contribution to it in the compute dtype
+    starts_stream = False
 
     def forward(self, tokens, step):
         raise NotImplementedError
@@ -41,6 +44,51 @@ class TokenEmbedding(Embedding):
     def forward(self, tokens, step):
         x = ops.embed(self.weight, tokens)
         return ops.cast(x, self.ctx.dtype) if x.dtype != self.ctx.dtype else x
+
+
+@register_part("embedding", "token_positional")
+class TokenPositionalEmbedding(Embedding):
+    """x[t] = N(E[ids[t]] + P[pos[t]]): a token table, a learned table of position
+    vectors (positions count from 0 in every sequence; neither term is scaled)
+    and an RMS norm over the sum (weight as it is, ``eps`` inside the root).  The
+    sum and the norm are 32-bit and the result is the 32-bit residual stream
+    itself (``starts_stream``), not a contribution to it.  ``names``: the tensors'
+    local names (keys token, position, norm)."""
+
+    starts_stream = True
+
+    def __init__(self, ctx: BuildContext, vocab: int, hidden: int, max_positions: int, eps: float,
+                 names: Optional[dict] = None):
+        super().__init__(ctx)
+        self.vocab, self.hidden, self.max_positions = int(vocab), int(hidden), int(max_positions)
+        self.eps = float(eps)
+        self.names = dict({"token": "weight", "position": "position.weight", "norm": "norm.weight"},
+                          **(names or {}))
+        self.weight = self.positions = self.norm_w = None
+
+    def param_specs(self):
+        nm = self.names
+        return {nm["token"]: ParamSpec((self.vocab, self.hidden)),
+                nm["position"]: ParamSpec((self.max_positions, self.hidden)),
+                nm["norm"]: ParamSpec((self.hidden,), "vector")}
+
+    def load(self, params):
+        nm = self.names
+        self.weight = params[nm["token"]].contiguous()
+        self.positions = params[nm["position"]].contiguous()
+        if self.positions.dtype != self.weight.dtype:
+            raise ValueError("the token and position tables must be stored in one dtype")
+        self.norm_w = params[nm["norm"]].float().contiguous()
+
+    def kernel_modules(self):
+        return ("embed",)
+
+    def captures_prompts(self):
+        return True
+
+    def forward(self, tokens, step):
+        return ops.embed_pos_norm(self.weight, self.positions, tokens, step.token_pos,
+                                  self.norm_w, self.eps)
 
 
 class Head(Part):

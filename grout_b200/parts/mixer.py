@@ -56,8 +56,15 @@ class GQAAttention(Mixer):
     logit (tensor ``sink`` [heads]) that stands in the softmax's denominator as
     exp(sink) beside the keys' terms and has no value; ``values_are_keys`` takes
     the values to be the keys as projected, before the rotation (there is no v
-    projection; the cache still holds both, the keys rotated).  ``names`` replaces
-    local tensor names (keys: q, k, v, o, q_norm, k_norm, sink).
+    projection; the cache still holds both, the keys rotated).  ``sink_logit`` puts
+    the same constant logit into every head's denominator instead of a learned one
+    (0.0: one is added to the sum of exponentials).  ``q_temp`` = (coef, every)
+    multiplies the query at position p, after its norm, by
+    1 + coef * ln(floor((p + 1) / every) + 1).  ``v_head_dim``: values of another
+    size than queries and keys; the cache, the queries and the attention's output
+    are then as wide as the larger of the two, filled up with zeros, and the o
+    projection's columns likewise, so that every attention kernel serves.
+    ``names`` replaces local tensor names (keys: q, k, v, o, q_norm, k_norm, sink).
     """
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
@@ -68,11 +75,28 @@ class GQAAttention(Mixer):
                  head_dim: int, position: PartSpec, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None, scale: Optional[float] = None,
                  shares_kv: bool = False, softcap: Optional[float] = None, sinks: bool = False,
-                 values_are_keys: bool = False, names: Optional[dict] = None):
+                 values_are_keys: bool = False, names: Optional[dict] = None,
+                 v_head_dim: Optional[int] = None, q_temp: Optional[tuple] = None,
+                 sink_logit: Optional[float] = None):
         super().__init__(ctx)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.nq, self.nkv, self.D = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.Dv = int(v_head_dim) if v_head_dim else self.D
+        # the width of a cached row, of a query and of the attention's output
+        self.Ds = max(self.D, self.Dv)
+        if self.Ds != self.D or self.Ds != self.Dv:
+            if values_are_keys or shares_kv:
+                raise ValueError("values of another size than the keys go with a v projection "
+                                 "and a cache of the layer's own")
+            if ctx.dtype == torch.bfloat16:       # the tensor-core kernels take multiples of 16
+                self.Ds = (self.Ds + 15) // 16 * 16
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        if self.q_temp and self.q_temp[1] <= 0:
+            raise ValueError("q_temp = (coef, every) with every >= 1")
+        if sink_logit is not None and sinks:
+            raise ValueError("either learned sinks or one constant sink logit")
+        self.sink_logit = None if sink_logit is None else float(sink_logit)
         self.qk_norm_eps = qk_norm_eps
         self.window = window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.D)
@@ -96,11 +120,11 @@ class GQAAttention(Mixer):
 
     def param_specs(self):
         H, nq, nkv, D, nm = self.hidden, self.nq, self.nkv, self.D, self.names
-        specs = {nm["q"]: ParamSpec((nq * D, H)), nm["o"]: ParamSpec((H, nq * D))}
+        specs = {nm["q"]: ParamSpec((nq * D, H)), nm["o"]: ParamSpec((H, nq * self.Dv))}
         if not self.shares_kv:
             specs[nm["k"]] = ParamSpec((nkv * D, H))
             if not self.values_are_keys:
-                specs[nm["v"]] = ParamSpec((nkv * D, H))
+                specs[nm["v"]] = ParamSpec((nkv * self.Dv, H))
         if self.qk_norm_eps is not None:
             specs[nm["q_norm"]] = ParamSpec((D,), "vector")
             if not self.shares_kv:
@@ -117,7 +141,14 @@ class GQAAttention(Mixer):
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must be stored in one dtype to be fused")
         self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
-        self.o = Linear(params[nm["o"]], self.ctx.products)
+        o = params[nm["o"]]
+        if self.Ds != self.Dv:      # zero columns where the attention's output is filled up
+            wide = o.new_zeros((self.hidden, self.nq, self.Ds))
+            wide[:, :, :self.Dv] = o.view(self.hidden, self.nq, self.Dv)
+            o = wide.view(self.hidden, self.nq * self.Ds)
+        self.o = Linear(o, self.ctx.products)
+        if self.sink_logit is not None:
+            self.sink = torch.full((self.nq,), self.sink_logit, dtype=torch.float32, device=o.device)
         if self.qk_norm_eps is not None:
             self.q_norm_w = params[nm["q_norm"]].contiguous()
             if not self.shares_kv:
@@ -128,11 +159,11 @@ class GQAAttention(Mixer):
     def kernel_modules(self):
         mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules() + self.o.kernel_modules()
         if self.ctx.dtype == torch.bfloat16:
-            mods += ops.fast_attention_modules(self.D, self.nq, self.nkv)
+            mods += ops.fast_attention_modules(self.Ds, self.nq, self.nkv)
         return mods
 
     def cache_spec(self):
-        return None if self.shares_kv else KVSpec(self.nkv, self.D, self.window)
+        return None if self.shares_kv else KVSpec(self.nkv, self.Ds, self.window)
 
     def captures_prompts(self):
         # an encoding with arithmetic of its own runs between two kernels here and
@@ -142,10 +173,13 @@ class GQAAttention(Mixer):
     def forward(self, x, step, cache):
         T = x.shape[0]
         rot = self.position.rotary()
-        if cache is None or (cache.spec.n_kv_heads, cache.spec.head_dim) != (self.nkv, self.D):
-            raise ValueError(f"attention with {self.nkv} kv heads of {self.D} was given the cache "
+        if cache is None or (cache.spec.n_kv_heads, cache.spec.head_dim) != (self.nkv, self.Ds):
+            raise ValueError(f"attention with {self.nkv} kv heads of {self.Ds} was given the cache "
                              f"{None if cache is None else cache.spec}")
         fused = rot is not None or type(self.position).apply_qk is PositionEncoding.apply_qk
+        if not fused and (self.Ds != self.D or self.q_temp):
+            raise ValueError("a position encoding with arithmetic of its own goes with neither "
+                             "values of another size nor a query temperature")
         # the q/k preparation can add the partial sums of a split-K projection itself
         qkv = self.qkv(x, partial_ok=fused and x.dtype == torch.bfloat16 and not self.shares_kv)
         if self.shares_kv:
@@ -153,13 +187,13 @@ class GQAAttention(Mixer):
                                   eps=self.qk_norm_eps or 0.0,
                                   inv_freq=rot.inv_freq if rot else None,
                                   rot_dim=rot.rot_dim if rot else 0, token_seq=step.token_seq,
-                                  token_pos=step.token_pos, slots=step.slots)
+                                  token_pos=step.token_pos, slots=step.slots, q_temp=self.q_temp)
             if rot is None:
                 q, _k = self.position.apply_qk(q, q[:, :0], step.token_pos)
             attn = ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
                                  step=step, page=cache.page, scale=self.scale, window=self.window,
                                  softcap=self.softcap, sinks=self.sink)
-            return self.o(attn.view(T, self.nq * self.D), partial_ok=True)
+            return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)
         common = dict(q_w=self.q_norm_w, k_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
                       values_are_keys=self.values_are_keys, token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)
         if fused:
@@ -167,7 +201,8 @@ class GQAAttention(Mixer):
                                   inv_freq=rot.inv_freq if rot else None,
                                   rot_dim=rot.rot_dim if rot else 0,
                                   block_table=cache.block_table, k_pages=cache.k_pages,
-                                  v_pages=cache.v_pages, page=cache.page, **common)
+                                  v_pages=cache.v_pages, page=cache.page, v_dim=self.Dv,
+                                  q_temp=self.q_temp, **common)
         else:
             # a position encoding with its own arithmetic: normalise, hand q and k
             # over, then store
@@ -182,4 +217,4 @@ class GQAAttention(Mixer):
         attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
                              page=cache.page, scale=self.scale, window=self.window,
                              softcap=self.softcap, sinks=self.sink)
-        return self.o(attn.view(T, self.nq * self.D), partial_ok=True)
+        return self.o(attn.view(T, self.nq * self.Ds), partial_ok=True)

@@ -11,8 +11,13 @@
   ``Contribution``: a sublayer's output that passes through a norm of its own and
   a constant factor on its way into the stream ("sandwich" layers), with, if the
   model has one, a vector that is added to every row on the same occasion.
-  ``LayerNorm`` does all of that in its one kernel as well; every other norm
-  resolves the contribution first and goes on as above.
+  ``LayerNorm`` does all of that in its one kernel as well, and so does ``RMSNorm``
+  for a contribution whose own norm is an RMS norm (with, if the layer has one, a
+  learned per-channel scale behind it); every other combination is resolved
+  first and goes on as above.
+* ``stream_add(res, delta, dtype) -> (res, x)``: the same sum without a norm
+  behind it, for sublayers that read the stream as it is: ``x`` is the updated
+  stream in the compute dtype.
 """
 from __future__ import annotations
 
@@ -28,14 +33,16 @@ from .base import BuildContext, ParamSpec, Part, register_part
 
 @dataclass
 class Contribution:
-    """What is about to be added to the residual stream: ``mult * norm(delta)``
+    """What is about to be added to the residual stream: ``mult * scale * norm(delta)``
     (just ``delta`` without a norm; nothing when ``delta`` is None) plus
     ``offset`` on every row.  ``delta`` is [T, N] in the compute dtype or a stack of
-    32-bit partial sums [S, T, N]; ``offset`` a 32-bit vector [N]."""
+    32-bit partial sums [S, T, N]; ``offset`` and ``scale`` (a learned factor per
+    channel, "layer scale") are 32-bit vectors [N]."""
     delta: Optional[torch.Tensor]
     norm: Optional["Norm"] = None
     mult: float = 1.0
     offset: Optional[torch.Tensor] = None
+    scale: Optional[torch.Tensor] = None
 
     def resolved(self) -> Optional[torch.Tensor]:
         """The contribution as one 32-bit tensor [T, N] (step by step, for norms
@@ -48,6 +55,8 @@ class Contribution:
                                   else ops.cast(d, self.norm.ctx.dtype))
         if d is not None:
             d = d.float() * self.mult if self.mult != 1.0 else d.float()
+            if self.scale is not None:
+                d = d * self.scale.float()[None, :]
         if self.offset is not None:
             d = self.offset.float()[None, :] if d is None else d + self.offset.float()[None, :]
         return d
@@ -59,7 +68,7 @@ def with_offset(pending, offset: torch.Tensor) -> Contribution:
     if isinstance(pending, Contribution):
         if pending.offset is not None:
             offset = pending.offset + offset
-        return Contribution(pending.delta, pending.norm, pending.mult, offset)
+        return Contribution(pending.delta, pending.norm, pending.mult, offset, pending.scale)
     return Contribution(pending, None, 1.0, offset)
 
 
@@ -98,16 +107,24 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * w; the weight multiplies as it is
     (src/kernels.rs:316-341, src/training.rs:233-238)."""
 
-    def __init__(self, ctx: BuildContext, dim: int, eps: float):
+    def __init__(self, ctx: BuildContext, dim: int, eps: float, name: str = "weight"):
         super().__init__(ctx)
-        self.dim, self.eps = int(dim), float(eps)
+        self.dim, self.eps, self.name = int(dim), float(eps), name
         self.weight = None
+        self._weight32 = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.dim,), "vector")}
+        return {self.name: ParamSpec((self.dim,), "vector")}
 
     def load(self, params):
-        self.weight = params["weight"].contiguous()
+        self.weight = params[self.name].contiguous()
+        self._weight32 = None
+
+    def weight32(self) -> torch.Tensor:
+        """The weight in 32-bit, as the kernels that take a whole contribution read it."""
+        if self._weight32 is None:
+            self._weight32 = self.weight.float().contiguous()
+        return self._weight32
 
     def kernel_modules(self):
         return ("norm",)
@@ -121,9 +138,39 @@ class RMSNorm(Norm):
         return y
 
     def add_norm(self, res, delta, rows=None):
-        if isinstance(delta, Contribution):      # resolved step by step, added in 32-bit
+        if isinstance(delta, Contribution):
+            if _one_kernel(delta):
+                return _add_contribution(res, delta, self.ctx.dtype, rows, self)
+            # resolved step by step, added in 32-bit
             res, delta = residual_add(res, delta.resolved()), None
         return ops.add_rmsnorm(res, delta, self.weight, self.eps, dtype=self.ctx.dtype, rows=rows)
+
+
+def _one_kernel(c: Contribution) -> bool:
+    """Whether ``ops.add_postnorm`` takes the contribution whole."""
+    return c.mult == 1.0 and c.offset is None and (c.norm is None or type(c.norm) is RMSNorm)
+
+
+def _add_contribution(res, c: Contribution, dtype, rows, norm: Optional[RMSNorm]):
+    post = c.norm if c.delta is not None else None
+    return ops.add_postnorm(res, c.delta, dtype=dtype, rows=rows,
+                            post_weight=post.weight32() if post else None,
+                            post_eps=post.eps if post else 0.0,
+                            scale=c.scale if c.delta is not None else None,
+                            weight=norm.weight32() if norm else None,
+                            eps=norm.eps if norm else 0.0)
+
+
+def stream_add(res, delta, dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Adds ``delta`` (a tensor in the compute dtype, a stack of partial sums, a
+    ``Contribution`` or None) into the 32-bit stream ``res`` (None: the stream
+    starts with the contribution) and returns the stream with its rounding to
+    ``dtype``, which is what a sublayer without a norm in front of it reads."""
+    if not isinstance(delta, Contribution):
+        delta = Contribution(delta)
+    if not _one_kernel(delta):
+        res, delta = residual_add(res, delta.resolved()), Contribution(None)
+    return _add_contribution(res, delta, dtype, None, None)
 
 
 @register_part("norm", "layernorm")
