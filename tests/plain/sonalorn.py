@@ -67,6 +67,7 @@ def short_conv(x, taps_w):
 def delta_rule(q, k, v, beta, decay):
     """One head.  q, k [T, dk]; v [T, dv]; beta, decay [T].  S starts at zero;
     per token S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+    q, k, v, beta, decay = (x.to(DT) for x in (q, k, v, beta, decay))
     T, dk = k.shape
     S = torch.zeros(dk, v.shape[1], dtype=DT)
     out = []
@@ -110,6 +111,7 @@ def query_temperature(positions, coef, every):
 
 def sink_attention(q, k, v, scale):
     """One head, causal; the denominator holds one more term exp(0) = 1."""
+    q, k, v = q.to(DT), k.to(DT), v.to(DT)
     s = (q @ k.T) * float(scale)
     T = q.shape[0]
     mask = torch.ones(T, T, dtype=torch.bool).tril()
@@ -205,3 +207,21 @@ def forward(cfg, W, tokens, return_layers=False):
         after.append(x.clone())
     logits = rms_norm(x, W["final.norm"], eps) @ W["head"].to(DT).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def logits(W, cfg, tokens, rows=None):
+    """Logits [T, vocab] of one sequence (or of the given rows)."""
+    out = forward(cfg, W, list(tokens))
+    return out if rows is None else out[list(rows)]
+
+
+def greedy_generate(W, cfg, prompt, n_new, stop_ids=()):
+    """The plain loop: the whole sequence again for every new token."""
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(cfg, W, seq)[-1]))
+        if tok in stop_ids:
+            break
+        out.append(tok)
+        seq.append(tok)
+    return out

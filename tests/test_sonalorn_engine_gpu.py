@@ -1,0 +1,387 @@
+"""The Sonalorn design through the engine against the plain implementation, in
+every way of cutting the work, on three small models that differ in every size and
+constant (and from layer to layer): the order of delta and attention layers,
+layers that run another layer's tensors, layers without feed-forward, values wider
+and narrower than keys, one to four taps, routers with and without groups and
+pass-through experts.  The random weights are reshaped so that faults show: slow
+and fast decays side by side, routers that are far from uniform with corrections
+that change the choice, experts whose clamps bite, queries sharp enough that the
+temperature and the sink move the result."""
+import json
+import os
+
+import pytest
+import torch
+
+from conftest import random_tokens
+from helpers import run_batch, run_chunks, run_schedule, run_tail_decoded, run_whole
+from plain import sonalorn as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+ROW_BAR = 0.08
+
+
+def assert_close(got, want, dtype, what=""):
+    """32-bit: element by element, at 1e-4 + 1e-3 |want| (the sharpened weights
+    carry 32-bit rounding to a few 1e-5 in the logits; a lost mechanism moves them
+    by more than 0.05).  bfloat16: a rounding that flips an expert or moves a sharp
+    attention weight changes single logits visibly while rows as a whole stay
+    close; the bar is on rows, the root mean square of a row's differences (mean
+    taken off) as a share of the logits' spread."""
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    if dtype == "float32":
+        err = (got - want).abs()
+        assert got.shape == want.shape and bool((err <= 1e-4 + 1e-3 * want.abs()).all()), (
+            f"{what}: max err {float(err.max()):.3g} at {int(err.argmax())}")
+        return
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    d = got - want
+    d = d - d.mean(dim=-1, keepdim=True)
+    spread = float((want - want.mean(dim=-1, keepdim=True)).pow(2).mean().sqrt())
+    rows = d.pow(2).mean(dim=-1).sqrt() / spread
+    # Rounding can flip a token's expert, or the sign of a read-out that is close to
+    # zero before its norm, and a normalised sublayer output carries such a change into
+    # the stream whole: single rows may be far off (the plain model with only its
+    # sublayers' inputs rounded to bfloat16 shows the same).  A lost mechanism, a wrong
+    # page or a lost state moves every row after it by more than 0.3, so the bar is on
+    # the median and the upper quartile.
+    med, q3 = float(rows.median()), float(rows.quantile(0.75))
+    assert med <= ROW_BAR and q3 <= 3 * ROW_BAR, (
+        f"{what}: median row differs by {med:.3f} of the logits' spread, upper quartile {q3:.3f}, "
+        f"worst {float(rows.max()):.3f} (row {int(rows.argmax())})")
+
+
+def _delta(**kw):
+    return dict(dict(heads=4, kv_heads=2, dim=16, vdim=8, conv=3), **kw)
+
+
+def _attn(**kw):
+    return dict(dict(heads=4, kv_heads=2, dim=16, vdim=16, scale=0.5, q_temp={"coef": 0.3, "every": 5}), **kw)
+
+
+def _moe(experts, identity, top, ff, limit, groups=None):
+    r = {"experts": experts, "identity": identity, "top": top}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": r}
+
+
+def _layer(kind, mixer, mlp, **kw):
+    return dict(type=kind, mixer=mixer, mlp=mlp, **kw)
+
+
+_X1 = _layer("attention", _attn(), _moe(6, 2, 3, 24, 0.6, (4, 2)))
+_Y1 = _layer("delta", _delta(heads=2, kv_heads=2, dim=64, vdim=32, conv=4), _moe(5, 0, 2, 40, 1.5))
+SON = {
+    # attention first; the last layer runs the first one's tensors; values wider than keys elsewhere
+    "S": dict(architecture="Sonalorn", vocab=211, width=64, max_positions=400, norm={"eps": 1e-5},
+              layers=[_X1, _layer("delta", _delta(), {"kind": "dense", "ff": 96}),
+                      _layer("attention", _attn(heads=2, kv_heads=1, dim=16, vdim=40, scale=0.3, q_temp=None), None),
+                      dict(_X1, weights_of=0)]),
+    # heads of 64 (the tensor-core attention kernels), delta heads of 64 x 32, four taps, one tap,
+    # a router without groups or pass-through experts, a layer without feed-forward
+    "T": dict(architecture="Sonalorn", vocab=300, width=128, max_positions=512, norm={"eps": 3e-6},
+              layers=[_Y1,
+                      _layer("attention", _attn(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.15,
+                                                q_temp={"coef": 1.0, "every": 64}), {"kind": "dense", "ff": 200}),
+                      _layer("delta", _delta(heads=3, kv_heads=1, dim=24, vdim=40, conv=1), None),
+                      dict(_Y1, weights_of=0)]),
+    # values narrower than keys, head size that is no multiple of 16, top 1 within one group of three
+    "U": dict(architecture="Sonalorn", vocab=160, width=96, max_positions=300, norm={"eps": 1e-6},
+              layers=[_layer("delta", _delta(heads=6, kv_heads=3, dim=40, vdim=12, conv=2), _moe(9, 3, 1, 16, 0.4, (3, 1))),
+                      _layer("attention", _attn(heads=6, kv_heads=2, dim=24, vdim=8, scale=0.4,
+                                                q_temp={"coef": 0.3, "every": 1}), {"kind": "dense", "ff": 64}),
+                      _layer("attention", _attn(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.1), None)]),
+}
+SEEDS = {"S": 11, "T": 13, "U": 17}
+LENGTHS = {"S": [1, 5, 70, 150], "T": [2, 64, 129, 300], "U": [3, 131, 270]}
+
+
+def _sharpen(tensors):
+    g = torch.Generator().manual_seed(1)
+    out = {}
+    for name, t in tensors:
+        f = t.float()
+        if name.endswith(".A_log"):
+            f = torch.linspace(-6.0, 0.5, f.numel())           # heads that keep and heads that forget
+        elif name.endswith(".conv"):
+            f = torch.randn(f.shape, generator=g) * 0.6
+        elif name.endswith(".router"):
+            f = f * 10.0
+        elif name.endswith(".correction"):
+            f = f * 1.5 - 0.08
+        elif ".mlp.e" in name and (name.endswith(".gate") or name.endswith(".up")):
+            f = f * 8.0                                         # the clamps bite
+        elif name.endswith(".mix.b") or name.endswith(".mix.a"):
+            f = f * 5.0
+        out[name] = f.to(t.dtype)
+    return out
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """name -> (folder, config dict, {tensor name: CPU tensor})."""
+    import grout_b200.architectures  # noqa: F401
+    from grout_b200.config import resolve_architecture
+    from grout_b200.engine.model import expected_tensors
+    from grout_b200.weights import random_tensors, write_safetensors
+    base = tmp_path_factory.mktemp("sonalorn")
+    out = {}
+    for name, cfg in SON.items():
+        arch = resolve_architecture(cfg)
+        exp = expected_tensors(arch.plan(arch.config_cls.from_dict(cfg)))
+        w = _sharpen(random_tensors(exp, SEEDS[name]))
+        folder = str(base / name)
+        os.makedirs(folder)
+        with open(os.path.join(folder, "config.json"), "w") as fh:
+            json.dump(cfg, fh)
+        write_safetensors(os.path.join(folder, "model.safetensors"), list(w.items()))
+        out[name] = (folder, cfg, w)
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(models):
+    from grout_b200.engine import Engine
+    made = {}
+
+    def get(name, dtype, **kw):
+        key = (name, dtype, tuple(sorted(kw.items())))
+        if key not in made:
+            made[key] = Engine.load(models[name][0], dtype=dtype, max_tokens=4096, max_batch=8,
+                                    max_seq_len=512, **kw)
+        return made[key]
+    return get
+
+
+@pytest.fixture(scope="module")
+def oracle(models):
+    memo = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in memo:
+            _d, cfg, w = models[name]
+            memo[key] = plain.logits(w, cfg, list(tokens))
+        return memo[key]
+    return get
+
+
+def test_the_sharpened_weights_do_what_they_are_for(models):
+    """A model on which a lost sink, temperature, correction, group rule, clamp,
+    pass-through expert, convolution tail or slow decay shows in the logits."""
+    _d, cfg, w = models["S"]
+    toks = random_tokens(60, cfg["vocab"], 1)
+    full = plain.logits(w, cfg, toks)
+
+    def moved(cfg2=None, w2=None):
+        return float((plain.logits(w2 or w, cfg2 or cfg, toks) - full).abs().max())
+
+    def with_layer0(**mixer):
+        c = json.loads(json.dumps(cfg))
+        c["layers"][0]["mixer"].update(mixer)
+        c["layers"][3]["mixer"].update(mixer)
+        return c
+
+    assert moved(with_layer0(q_temp={"coef": 0.3, "every": 6})) > 0.02
+    assert moved(with_layer0(q_temp=None)) > 0.05
+    c = json.loads(json.dumps(cfg))
+    for i in (0, 3):
+        c["layers"][i]["mlp"]["router"]["groups"] = {"count": 4, "keep": 4}
+    assert moved(c) > 0.05
+    c = json.loads(json.dumps(cfg))
+    for i in (0, 3):
+        c["layers"][i]["mlp"]["expert"]["limit"] = 6.0
+    assert moved(c) > 0.05
+    assert moved(w2={k: (v * 0 if k.endswith(".correction") else v) for k, v in w.items()}) > 0.05
+    assert moved(w2={k: (v - 3.0 if k.endswith(".A_log") else v) for k, v in w.items()}) > 0.05
+    tail_off = {k: v.clone() for k, v in w.items()}
+    for k in tail_off:
+        if k.endswith(".conv"):
+            tail_off[k][:, :-1] = 0
+    assert moved(w2=tail_off) > 0.05
+    # the sink: without it a first token's attention output would be its value whole
+    h = torch.randn(1, cfg["width"], dtype=torch.float64)
+    m = cfg["layers"][0]["mixer"]
+    y = plain.attention_mixer(h, w, "l0.mix.", m, 1e-5)
+    v = (h @ w["l0.mix.v"].double().T).view(m["kv_heads"], m["vdim"]).repeat_interleave(2, 0).reshape(1, -1)
+    assert float((y - v @ w["l0.mix.o"].double().T).abs().max()) > 1e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SON))
+def test_each_request_alone_and_whole(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    for i, n in enumerate(LENGTHS[name]):
+        toks = random_tokens(n, SON[name]["vocab"], 100 + i)
+        assert_close(run_whole(eng, toks), oracle(name, toks), dtype, f"{name} whole, {n} tokens")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SON))
+def test_prefill_against_token_by_token(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    n = LENGTHS[name][-1]
+    toks = random_tokens(n, SON[name]["vocab"], 200)
+    assert_close(run_tail_decoded(eng, toks, tail=40), oracle(name, toks), dtype, f"{name} tail")
+    short = toks[:90]
+    got = run_tail_decoded(eng, short, tail=89)
+    assert_close(got, oracle(name, short), dtype, f"{name} decoded from the first token")
+    if dtype == "float32":
+        assert (got - run_whole(eng, short)).abs().max().item() < 2e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SON))
+def test_a_prompt_fed_in_portions(engines, oracle, name, dtype):
+    """Portions of two tokens and of one (shorter than the convolutions' tail);
+    portions that end one short of a page, on it and beyond it."""
+    eng = engines(name, dtype)
+    for i, chunks in enumerate([[2] * 12 + [1, 3], [63, 1, 64, 2], [60, 10, 70], [1, 1, 1, 2, 1, 30, 1, 1]]):
+        toks = random_tokens(sum(chunks), SON[name]["vocab"], 700 + i)
+        got = run_chunks(eng, toks, chunks)
+        assert_close(got, oracle(name, toks), dtype, f"{name} portions {chunks}")
+        if dtype == "float32":
+            assert (got - run_whole(eng, toks)).abs().max().item() < 2e-5, chunks
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SON))
+def test_unequal_batches_one_after_another(engines, oracle, name, dtype):
+    """Three batches in a row on one engine: slots (and with them the delta rule's
+    state rows) and pages of an earlier batch are used again by a later one, and
+    within a batch the shorter requests end earlier."""
+    eng = engines(name, dtype)
+    V = SON[name]["vocab"]
+    plans = [[(5, 3), (11, 9), (17, 1)],
+             [(1, 20), (7, 2), (30, 11), (64, 5), (130, 33), (200, 80)],
+             [(65, 4), (2, 4), (128, 70)]]
+    for b, plan in enumerate(plans):
+        reqs = [random_tokens(p + d, V, 300 + 10 * b + i) for i, (p, d) in enumerate(plan)]
+        got = run_batch(eng, reqs, [p for p, _ in plan])
+        for i, r in enumerate(reqs):
+            assert_close(got[i], oracle(name, r), dtype, f"{name} batch {b} request {i}")
+            if dtype == "float32":
+                assert (got[i] - run_whole(eng, r)).abs().max().item() < 2e-5, (b, i)
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["S", "T"])
+def test_first_tokens_and_long_decoding(engines, oracle, name, dtype):
+    """A prompt of one token and 250 decoded ones: the first positions (a sink beside
+    a single key, a convolution that still sees zeros, an empty state) and a long
+    run of single steps across page boundaries."""
+    eng = engines(name, dtype)
+    toks = random_tokens(251, SON[name]["vocab"], 400)
+    assert_close(run_tail_decoded(eng, toks, tail=250), oracle(name, toks), dtype, "long decoding")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SON))
+def test_steps_that_mix_one_and_many_tokens(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    lengths = [20 + 5 + 1 + 3 + 1, 9 + 1 + 1 + 1 + 1 + 1, 70 + 1 + 2]
+    schedule = [{0: 20, 1: 9}, {0: 5, 1: 1}, {0: 1, 1: 1, 2: 70}, {0: 3, 1: 1, 2: 1},
+                {0: 1, 1: 1, 2: 2}, {1: 1}]
+    reqs = [random_tokens(n, SON[name]["vocab"], 720 + i) for i, n in enumerate(lengths)]
+    got = run_schedule(eng, reqs, schedule)
+    for i, r in enumerate(reqs):
+        assert_close(got[i], oracle(name, r), dtype, f"{name} mixed steps, request {i}")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_captured_steps_against_steps_launched_one_by_one(engines, oracle, dtype):
+    """Bit-equal in 32-bit; both within the plain implementation's bar in bfloat16."""
+    reqs = [random_tokens(n, SON["T"]["vocab"], 740 + i) for i, n in enumerate((90, 33, 140))]
+    outs = {}
+    for use in (True, False):
+        eng = engines("T", dtype, use_graphs=use)
+        outs[use] = run_batch(eng, reqs, [60, 30, 100])
+    for i, r in enumerate(reqs):
+        assert_close(outs[True][i], oracle("T", r), dtype, f"captured, request {i}")
+        assert_close(outs[False][i], oracle("T", r), dtype, f"launched, request {i}")
+        if dtype == "float32":
+            assert torch.equal(outs[True][i], outs[False][i])
+
+
+@pytest.mark.parametrize("name", sorted(SON))
+def test_greedy_generation_through_the_engine(models, name):
+    """Engine.generate (its scheduler, cache and device sampler) against the plain
+    loop, in 32-bit, where the argmax is the same token."""
+    from grout_b200.engine import Engine
+    folder, cfg, w = models[name]
+    eng = Engine.load(folder, dtype="float32", max_tokens=2048, max_batch=3)
+    prompts = [random_tokens(n, cfg["vocab"], 800 + i) for i, n in enumerate((1, 7, 30, 64, 5))]
+    want = [plain.greedy_generate(w, cfg, p, 10) for p in prompts]
+    outs = eng.generate(prompts, 10, ignore_eos=True)          # five requests on three slots
+    assert [o.token_ids for o in outs] == want
+    stop = want[1][3]
+    outs = eng.generate(prompts, 10, stop_ids=[stop])
+    assert [o.token_ids for o in outs] == [plain.greedy_generate(w, cfg, p, 10, stop_ids=(stop,))
+                                           for p in prompts]
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+def test_generation_in_bfloat16_and_the_command_line(models, tmp_path):
+    """bfloat16 generation runs through captured steps; its tokens are the plain
+    loop's wherever the plain logits leave no doubt.  And the command line serves
+    the design as it serves the others."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    from grout_b200.engine import Engine
+    folder, cfg, w = models["T"]
+    eng = Engine.load(folder, dtype="bfloat16", max_tokens=2048, max_batch=4)
+    prompt = random_tokens(70, cfg["vocab"], 820)
+    got = eng.generate([prompt], 10, ignore_eos=True)[0].token_ids
+    seq = list(prompt)
+    for tok in got:
+        row = plain.logits(w, cfg, seq, rows=[len(seq) - 1])[0]
+        top2 = torch.topk(row, 2).values
+        if float(top2[0] - top2[1]) > 0.1 * float(row.std()):
+            assert tok == int(torch.argmax(row)), len(seq)
+        seq.append(tok)
+    out = tmp_path / "out.json"
+    ids = ",".join(str(t) for t in prompt[:9])
+    r = subprocess.run([sys.executable, "-m", "grout_b200", "--model", folder, "--prompt-ids", ids,
+                        "--max-new-tokens", "6", "--ignore-eos", "--fp32", "--device-argmax",
+                        "--output-json", str(out), "--quiet"], cwd=ROOT, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.load(open(out))["token_ids"] == plain.greedy_generate(w, cfg, prompt[:9], 6)
+
+
+def test_trace_replay_serves_the_design(models, tmp_path):
+    """bin/trace_run on a Sonalorn folder: a prompt, then single tokens, two requests."""
+    import subprocess
+    import sys
+    import numpy as np
+    from conftest import ROOT
+    folder, cfg, w = models["S"]
+    a, b = random_tokens(40, cfg["vocab"], 840), random_tokens(9, cfg["vocab"], 841)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:37], "want": [0, 36]},
+                                     {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [a[37]], "want": []},
+                                     {"id": "b", "tokens": [b[8]], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": [a[38]], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": [a[39]], "want": [0]}], "end": ["a"]}]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                        "--dtype", "float32", "--out", str(tmp_path), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    la, lb = plain.logits(w, cfg, a), plain.logits(w, cfg, b)
+    want = {0: torch.stack([la[0], la[36], lb[7]]), 1: lb[8:9], 2: la[38:39], 3: la[39:40]}
+    for i, wnt in want.items():
+        got = torch.from_numpy(np.fromfile(tmp_path / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"]))
+        assert_close(got, wnt, "float32", f"step {i}")
