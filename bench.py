@@ -21,9 +21,9 @@ weights, far more than the 126 MB L2, so nothing is flushed between timed steps.
                                        decode steps (launched one by one, an event pair
                                        around each): calls, time, GB/s, TFLOP/s, fractions
     python bench.py --requests S       the reference's request grid
-    python bench.py --designs [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
-                                       prefill and decode throughput of the Suvazen design beside
-                                       the Qwen3 decoder at equal layer sizes (random weights), and
+    python bench.py --designs [--design suvazen|sonalorn] [--design-sizes 1b,4b,8b] [--batch B] [--design-ops]
+                                       prefill and decode throughput of the Suvazen (or Sonalorn)
+                                       design beside the Qwen3 decoder at equal layer sizes (random weights), and
                                        with --design-ops the per-kernel tables of both
 """
 import argparse
@@ -183,7 +183,27 @@ DESIGN_SIZES = {"1b": (2048, 16, 8, 128, 6144, 16, 65536),
                 "8b": (4096, 32, 8, 128, 12288, 36, 151936)}
 
 
-def design_configs(size: str):
+def sonalorn_config(size: str) -> dict:
+    """The Sonalorn model of a size: the width, heads, head size, layers and vocabulary of
+    the Qwen3 model; of every four layers three mix by the gated delta rule (as many heads
+    as the attention has, keys and values of the head size, four taps) and one by
+    attention; every other layer has a dense feed-forward of the same rows and the rest
+    route two of eight experts of a quarter of the rows each (plus one pass-through
+    output, three groups of which two are kept): the weights a token uses are below the
+    Qwen3 model's, the weights held are above them."""
+    W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
+    delta = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, conv=4)
+    attn = dict(heads=nq, kv_heads=nkv, dim=D, vdim=D, scale=D ** -0.5, q_temp={"coef": 0.1, "every": 256})
+    dense = {"kind": "dense", "ff": I}
+    moe = {"kind": "moe", "expert": {"ff": I // 4 // 64 * 64, "limit": 7.0},
+           "router": {"experts": 8, "identity": 1, "top": 2, "groups": {"count": 3, "keep": 2}}}
+    layers = [dict(type="attention" if i % 4 == 3 else "delta", mixer=attn if i % 4 == 3 else delta,
+                   mlp=dense if i % 2 == 0 else moe) for i in range(L)]
+    return dict(architecture="Sonalorn", vocab=V, width=W, max_positions=CONTEXT, norm={"eps": 1e-6},
+                layers=layers)
+
+
+def design_configs(size: str, design: str = "suvazen"):
     W, nq, nkv, D, I, L, V = DESIGN_SIZES[size]
     qwen = dict(QWEN3_4B, hidden_size=W, num_attention_heads=nq, num_key_value_heads=nkv, head_dim=D,
                 intermediate_size=I, num_hidden_layers=L, vocab_size=V, tie_word_embeddings=False)
@@ -194,10 +214,13 @@ def design_configs(size: str):
                logit_scale=0.25, logit_softcap=30.0, loop={"start": 2, "stop": 4, "times": 1},
                layers=[dict(type="attention", mixer=mixer, mlp={"kind": "dense", "ff": 3 * I // 2})
                        for _ in range(L)])
+    if design == "sonalorn":
+        return {"qwen3": qwen, "sonalorn": sonalorn_config(size)}
     return {"qwen3": qwen, "suvazen": suv}
 
 
-def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) -> int:
+def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk,
+                which: str = "suvazen") -> int:
     """Prefill of one 2,048-token prompt and decode steps of ``batch`` sequences that hold such
     prompts, for both designs at each size: device times between CUDA events, the prompt step
     as the median of six after three, the decode steps as generation runs them (tokens chosen
@@ -208,7 +231,7 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) ->
     out = {}
     for size in sizes:
         out[size] = {}
-        for design, cfg in design_configs(size).items():
+        for design, cfg in design_configs(size, which).items():
             V = cfg.get("vocab_size", cfg.get("vocab"))
             room = (PROMPT + warm + steps + 64 + 63) // 64 * 64
             eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * room, max_batch=batch,
@@ -252,7 +275,9 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) ->
             dec_ms = a.elapsed_time(b) / steps
             n_weights = sum(t.numel() for t in _weights_of(eng))
             kv_bytes = sum(st.k[:, :1].numel() * 2 * 2 // 64 for st in eng.cache.stores if hasattr(st, "k"))
-            step_bytes = 2 * n_weights + batch * (PROMPT + warm + steps / 2) * kv_bytes
+            # a recurrent mixer reads and writes its whole state every step
+            state_bytes = sum(2 * st.state[:, :1].numel() * 4 for st in eng.cache.stores if hasattr(st, "state"))
+            step_bytes = 2 * n_weights + batch * ((PROMPT + warm + steps / 2) * kv_bytes + state_bytes)
             out[size][design] = {
                 "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PROMPT / pre_ms * 1e3, 1),
                 "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1),
@@ -294,7 +319,7 @@ def run_designs(sizes, batch: int, steps: int, warm: int, with_ops: bool, pk) ->
             eng.check()
             del eng, logits
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": "prefill and decode throughput, Suvazen beside Qwen3 at equal layer sizes",
+    print(json.dumps({"metric": f"prefill and decode throughput, {which.capitalize()} beside Qwen3 at equal layer sizes",
                       "unit": "tok/s", "dtype": "bf16", "data": "synthetic", "batch": batch,
                       "prompt_len": PROMPT, "steps": steps, "warmup": warm, "peaks": pk["source"],
                       "sizes": out}))
@@ -475,6 +500,8 @@ def main() -> int:
     ap.add_argument("--designs", action="store_true",
                     help="instead of the default run: the Suvazen design beside the Qwen3 decoder at "
                          "equal layer sizes (--design-sizes), prefill and decode at --batch")
+    ap.add_argument("--design", default="suvazen", choices=["suvazen", "sonalorn"],
+                    help="which design --designs sets beside Qwen3")
     ap.add_argument("--design-sizes", default="1b,4b,8b",
                     help=f"which of {sorted(DESIGN_SIZES)} --designs runs")
     ap.add_argument("--design-ops", action="store_true",
@@ -497,7 +524,7 @@ def main() -> int:
             print(f"bench.py: --design-sizes takes {sorted(DESIGN_SIZES)}", file=sys.stderr)
             return 2
         return run_designs(sizes, args.batch, min(args.steps, 64), max(args.warmup, 3), args.design_ops,
-                           peaks())
+                           peaks(), args.design)
     if args.prompt_len != PROMPT:
         if not 1 <= args.prompt_len <= 36864:
             print("bench.py: --prompt-len must be 1..36864", file=sys.stderr)

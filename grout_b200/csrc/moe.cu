@@ -19,7 +19,7 @@
 // weighted results are left as `top` 32-bit partial sums [top, T, W]
 // (choice j of token t in out[j, t, :]), which the norm that follows adds in
 // order.
-#include "common.cuh"
+#include "attn_mma.cuh"
 
 struct MoeArgs {
   const void* x;            // [T, W] activations
@@ -130,17 +130,18 @@ __global__ void moe_sort_kernel(const MoeArgs a) {
 #define MOE_BN 64
 #define MOE_BK 32
 
-// Which expert and which of its tiles of MOE_BM pairs block `b` has; false beyond the last.
+// Which expert and which of its tiles of BM pairs block `b` has; false beyond the last.
+template <int BM = MOE_BM>
 __device__ __forceinline__ bool moe_find_tile(const int* offsets, int E, int b, int& e_out,
                                               int& first, int& n_rows) {
   int tiles = 0;
   for (int e = 0; e < E; ++e) {
     const int cnt = offsets[e + 1] - offsets[e];
-    const int nt = (cnt + MOE_BM - 1) / MOE_BM;
+    const int nt = (cnt + BM - 1) / BM;
     if (b < tiles + nt) {
       e_out = e;
-      first = offsets[e] + (b - tiles) * MOE_BM;
-      n_rows = min(MOE_BM, offsets[e + 1] - first);
+      first = offsets[e] + (b - tiles) * BM;
+      n_rows = min(BM, offsets[e + 1] - first);
       return true;
     }
     tiles += nt;
@@ -251,6 +252,126 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
   }
 }
 
+
+// ---- the two products on the tensor cores (bfloat16, widths that are multiples of 8) ----
+// A block of four warps takes a tile of 64 pairs and 64 output columns; a warp owns 16 of
+// the rows and all 64 columns (mma.sync m16n8k16, 32-bit sums).  Rows of the activations
+// (gathered by token for the first product, in list order for the second) and rows of the
+// expert's weight reach shared memory by 16-byte asynchronous copies, two stages of 32
+// columns of the inner size; rows and columns beyond the tile's end are filled with zeros.
+// The first product runs gate and up side by side and applies the expert's activation to
+// its 32-bit sums; the second multiplies by the pair's weight and stores 32-bit.
+#define MT_BM 64
+#define MT_BN 64
+#define MT_BK 32
+#define MT_LD (MT_BK + 8)
+
+template <bool UP>
+__global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
+  constexpr int NB = UP ? 2 : 1;
+  __shared__ __align__(16) bf16 As[2][MT_BM * MT_LD];
+  __shared__ __align__(16) bf16 Bs[2][NB][MT_BN * MT_LD];
+  __shared__ int src_row[MT_BM];
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  int e, first, n_rows;
+  if (!moe_find_tile<MT_BM>(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K = UP ? a.W : a.F, N = UP ? a.F : a.W;
+  const int n0 = blockIdx.y * MT_BN;
+  if (tid < MT_BM) {
+    int r = -1;
+    if (tid < n_rows) r = UP ? a.perm[first + tid] / a.top : first + tid;
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const bf16* A = (const bf16*)(UP ? a.x : a.act);
+  const bf16* B0 = (const bf16*)(UP ? a.w_gate : a.w_down) + (size_t)e * N * K;
+  const bf16* B1 = UP ? (const bf16*)a.w_up + (size_t)e * N * K : nullptr;
+  auto load = [&](int stage, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {            // 64 rows x 4 pieces of 8 elements
+      const int c = tid + i * 128, r = c >> 2, kc = k0 + (c & 3) * 8;
+      const bool ok = src_row[r] >= 0 && kc < K;
+      cp_async16(&As[stage][r * MT_LD + (c & 3) * 8], ok ? A + (size_t)src_row[r] * K + kc : A, ok);
+      const bool okb = n0 + r < N && kc < K;
+      cp_async16(&Bs[stage][0][r * MT_LD + (c & 3) * 8], okb ? B0 + (size_t)(n0 + r) * K + kc : B0, okb);
+      if (UP) cp_async16(&Bs[stage][NB - 1][r * MT_LD + (c & 3) * 8],
+                         okb ? B1 + (size_t)(n0 + r) * K + kc : B1, okb);
+    }
+    cp_async_commit();
+  };
+  float acc[NB][8][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) acc[b][j][x] = 0.f;
+  const int arow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+  const int brow = (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
+  const int nk = (K + MT_BK - 1) / MT_BK;
+  load(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int st = kt & 1;
+    if (kt + 1 < nk) {
+      load(st ^ 1, (kt + 1) * MT_BK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MT_BK / 16; ++k) {
+      uint32_t af[4];
+      ldmatrix_x4(af, &As[st][arow * MT_LD + k * 16 + acol]);
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, &Bs[st][b][(j * 8 + brow) * MT_LD + k * 16 + bcol]);
+          mma_16816(acc[b][j], af, bf[0], bf[1]);
+          mma_16816(acc[b][j + 1], af, bf[2], bf[3]);
+        }
+    }
+    __syncthreads();   // the stage is refilled by the next turn's copies
+  }
+  pdl_launch_dependents_if_large();
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = warp * 16 + g + half * 8;
+    if (row >= n_rows) continue;
+    if (UP) {
+      bf16* dst = (bf16*)a.act + (size_t)(first + row) * N;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int col = n0 + j * 8 + t * 2;
+        float y[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const float gt = fminf(acc[0][j][half * 2 + x], a.limit);
+          const float up = fminf(fmaxf(acc[NB - 1][j][half * 2 + x], -a.limit), a.limit);
+          y[x] = gt / (1.0f + expf(-a.slope * gt)) * (up + 1.0f);
+        }
+        if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(y[0], y[1]);
+        else if (col < N) dst[col] = from_f32<bf16>(y[0]);
+      }
+    } else {
+      const int p = a.perm[first + row], tok = p / a.top, jc = p % a.top;
+      const float w = a.wts[p];
+      float* dst = a.out + ((size_t)jc * a.T + tok) * N;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int col = n0 + j * 8 + t * 2;
+        if (col + 1 < N) *reinterpret_cast<float2*>(dst + col) = make_float2(w * acc[0][j][half * 2], w * acc[0][j][half * 2 + 1]);
+        else if (col < N) dst[col] = w * acc[0][j][half * 2];
+      }
+    }
+  }
+}
+
 static int moe_check(const MoeArgs& a) {
   if (a.T < 0 || a.W <= 0 || a.F <= 0 || a.E <= 0 || a.n_identity < 0 || a.top <= 0 ||
       a.n_groups <= 0 || a.keep_groups <= 0 || a.keep_groups > a.n_groups)
@@ -276,6 +397,15 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
   if (e) return e;
   // the most tiles the pairs can make: every expert may end in a tile that is not full
   const long long pairs = (long long)a.T * a.top;
+  if (sizeof(T) == 2 && a.W % 8 == 0 && a.F % 8 == 0 &&
+      ((((uintptr_t)a.x) | ((uintptr_t)a.act) | ((uintptr_t)a.w_gate) | ((uintptr_t)a.w_up) |
+        ((uintptr_t)a.w_down) | ((uintptr_t)a.out)) & 15) == 0) {
+    const long long tc_tiles = pairs / MT_BM + (pairs < a.E ? pairs : a.E);
+    if (tc_tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;
+    e = gb_launch(moe_tc_kernel<true>, dim3((unsigned)tc_tiles, (a.F + MT_BN - 1) / MT_BN), dim3(128), 0, s, a);
+    if (e) return e;
+    return gb_launch(moe_tc_kernel<false>, dim3((unsigned)tc_tiles, (a.W + MT_BN - 1) / MT_BN), dim3(128), 0, s, a);
+  }
   const long long tiles = pairs / MOE_BM + (pairs < a.E ? pairs : a.E);
   if (tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;
   e = gb_launch(moe_up_kernel<T>, dim3((unsigned)tiles, (a.F + MOE_BN - 1) / MOE_BN), dim3(256), 0, s, a);
