@@ -425,7 +425,8 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
     ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
                  and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()),
                 key=lambda e: e.time_range.start)
-    starts = [i for i, e in enumerate(ev) if "embed_kernel" in e.name]
+    # a step begins with its embedding kernel, whichever the model has
+    starts = [i for i, e in enumerate(ev) if "embed_kernel" in e.name or "embed_pos_norm_kernel" in e.name]
     rows, total = {}, 0.0
     for a, b in zip(starts, starts[1:] + [len(ev)]):
         frontier = ev[a].time_range.start

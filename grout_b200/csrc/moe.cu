@@ -254,32 +254,42 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
 
 
 // ---- the two products on the tensor cores (bfloat16, widths that are multiples of 8) ----
-// A block of four warps takes a tile of 64 pairs and 64 output columns; a warp owns 16 of
-// the rows and all 64 columns (mma.sync m16n8k16, 32-bit sums).  Rows of the activations
+// A block of four warps takes a tile of BM pairs and 64 output columns (mma.sync m16n8k16,
+// 32-bit sums).  With BM = 64 (many tokens) a warp owns 16 of the rows and all 64 columns;
+// with BM = 16 (a decode step: a handful of pairs per expert, the weights' bytes are the
+// cost) the warps share the 16 rows and take 16 columns each.  Rows of the activations
 // (gathered by token for the first product, in list order for the second) and rows of the
-// expert's weight reach shared memory by 16-byte asynchronous copies, two stages of 32
-// columns of the inner size; rows and columns beyond the tile's end are filled with zeros.
-// The first product runs gate and up side by side and applies the expert's activation to
-// its 32-bit sums; the second multiplies by the pair's weight and stores 32-bit.
-#define MT_BM 64
+// expert's weight reach shared memory by 16-byte asynchronous copies, STAGES chunks of 64
+// columns of the inner size in flight; rows and columns beyond the tile's end are filled
+// with zeros.  The first product runs gate and up side by side and applies the expert's
+// activation to its 32-bit sums; the second multiplies by the pair's weight and stores 32-bit.
 #define MT_BN 64
-#define MT_BK 32
+#define MT_BK 64
 #define MT_LD (MT_BK + 8)
 
-template <bool UP>
+template <bool UP, int BM>
+struct MoeTile {
+  static constexpr int NB = UP ? 2 : 1;
+  static constexpr int STAGES = BM == 64 ? 3 : 4;
+  static constexpr int STAGE_ELEMS = (BM + NB * MT_BN) * MT_LD;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_ELEMS * sizeof(bf16);
+};
+
+template <bool UP, int BM>
 __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
-  constexpr int NB = UP ? 2 : 1;
-  __shared__ __align__(16) bf16 As[2][MT_BM * MT_LD];
-  __shared__ __align__(16) bf16 Bs[2][NB][MT_BN * MT_LD];
-  __shared__ int src_row[MT_BM];
+  using Tile = MoeTile<UP, BM>;
+  constexpr int NB = Tile::NB, STAGES = Tile::STAGES;
+  constexpr int NJ = BM == 64 ? 8 : 2;          // 8-column pieces of a warp's share
+  extern __shared__ __align__(16) bf16 tiles[];
+  __shared__ int src_row[BM];
   pdl_launch_dependents_if_small();
   pdl_wait();
   int e, first, n_rows;
-  if (!moe_find_tile<MT_BM>(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
+  if (!moe_find_tile<BM>(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = UP ? a.W : a.F, N = UP ? a.F : a.W;
   const int n0 = blockIdx.y * MT_BN;
-  if (tid < MT_BM) {
+  if (tid < BM) {
     int r = -1;
     if (tid < n_rows) r = UP ? a.perm[first + tid] / a.top : first + tid;
     src_row[tid] = r;
@@ -289,65 +299,71 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   const bf16* B0 = (const bf16*)(UP ? a.w_gate : a.w_down) + (size_t)e * N * K;
   const bf16* B1 = UP ? (const bf16*)a.w_up + (size_t)e * N * K : nullptr;
   auto load = [&](int stage, int k0) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {            // 64 rows x 4 pieces of 8 elements
-      const int c = tid + i * 128, r = c >> 2, kc = k0 + (c & 3) * 8;
+    bf16* As = tiles + stage * Tile::STAGE_ELEMS;
+    bf16* Bs = As + BM * MT_LD;
+    for (int c = tid; c < BM * 8; c += 128) {            // rows x 8 pieces of 8 elements
+      const int r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
       const bool ok = src_row[r] >= 0 && kc < K;
-      cp_async16(&As[stage][r * MT_LD + (c & 3) * 8], ok ? A + (size_t)src_row[r] * K + kc : A, ok);
-      const bool okb = n0 + r < N && kc < K;
-      cp_async16(&Bs[stage][0][r * MT_LD + (c & 3) * 8], okb ? B0 + (size_t)(n0 + r) * K + kc : B0, okb);
-      if (UP) cp_async16(&Bs[stage][NB - 1][r * MT_LD + (c & 3) * 8],
-                         okb ? B1 + (size_t)(n0 + r) * K + kc : B1, okb);
+      cp_async16(As + r * MT_LD + pc, ok ? A + (size_t)src_row[r] * K + kc : A, ok);
     }
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < MT_BN * 8 / 128; ++i) {
+      const int c = tid + i * 128, r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
+      const bool ok = n0 + r < N && kc < K;
+      cp_async16(Bs + r * MT_LD + pc, ok ? B0 + (size_t)(n0 + r) * K + kc : B0, ok);
+      if (UP) cp_async16(Bs + (MT_BN + r) * MT_LD + pc, ok ? B1 + (size_t)(n0 + r) * K + kc : B1, ok);
+    }
   };
-  float acc[NB][8][4];
+  float acc[NB][NJ][4];
 #pragma unroll
   for (int b = 0; b < NB; ++b)
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int x = 0; x < 4; ++x) acc[b][j][x] = 0.f;
-  const int arow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
-  const int brow = (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
+  const int row_w = BM == 64 ? warp * 16 : 0, col_w = BM == 64 ? 0 : warp * 16;
+  const int arow = row_w + (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+  const int brow = col_w + (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
   const int nk = (K + MT_BK - 1) / MT_BK;
-  load(0, 0);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {      // a group per stage, empty beyond the end
+    if (st < nk) load(st, st * MT_BK);
+    cp_async_commit();
+  }
   for (int kt = 0; kt < nk; ++kt) {
-    const int st = kt & 1;
-    if (kt + 1 < nk) {
-      load(st ^ 1, (kt + 1) * MT_BK);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<STAGES - 2>();                  // chunk kt has landed
+    __syncthreads();                              // ... for every thread; chunk kt - 1 is done with
+    if (kt + STAGES - 1 < nk) load((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * MT_BK);
+    cp_async_commit();
+    const bf16* As = tiles + (kt % STAGES) * Tile::STAGE_ELEMS;
+    const bf16* Bs = As + BM * MT_LD;
 #pragma unroll
     for (int k = 0; k < MT_BK / 16; ++k) {
       uint32_t af[4];
-      ldmatrix_x4(af, &As[st][arow * MT_LD + k * 16 + acol]);
+      ldmatrix_x4(af, As + arow * MT_LD + k * 16 + acol);
 #pragma unroll
       for (int b = 0; b < NB; ++b)
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
+        for (int j = 0; j < NJ; j += 2) {
           uint32_t bf[4];
-          ldmatrix_x4(bf, &Bs[st][b][(j * 8 + brow) * MT_LD + k * 16 + bcol]);
+          ldmatrix_x4(bf, Bs + (b * MT_BN + j * 8 + brow) * MT_LD + k * 16 + bcol);
           mma_16816(acc[b][j], af, bf[0], bf[1]);
           mma_16816(acc[b][j + 1], af, bf[2], bf[3]);
         }
     }
-    __syncthreads();   // the stage is refilled by the next turn's copies
   }
+  cp_async_wait<0>();
   pdl_launch_dependents_if_large();
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int row = warp * 16 + g + half * 8;
+    const int row = row_w + g + half * 8;
     if (row >= n_rows) continue;
     if (UP) {
       bf16* dst = (bf16*)a.act + (size_t)(first + row) * N;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int col = n0 + j * 8 + t * 2;
+      for (int j = 0; j < NJ; ++j) {
+        const int col = n0 + col_w + j * 8 + t * 2;
         float y[2];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -363,13 +379,24 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
       const float w = a.wts[p];
       float* dst = a.out + ((size_t)jc * a.T + tok) * N;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int col = n0 + j * 8 + t * 2;
+      for (int j = 0; j < NJ; ++j) {
+        const int col = n0 + col_w + j * 8 + t * 2;
         if (col + 1 < N) *reinterpret_cast<float2*>(dst + col) = make_float2(w * acc[0][j][half * 2], w * acc[0][j][half * 2 + 1]);
         else if (col < N) dst[col] = w * acc[0][j][half * 2];
       }
     }
   }
+}
+
+template <bool UP, int BM>
+static int moe_tc_launch(const MoeArgs& a, long long pairs, cudaStream_t s) {
+  const long long tiles = pairs / BM + (pairs < a.E ? pairs : a.E);
+  if (tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;
+  const size_t smem = MoeTile<UP, BM>::SMEM;
+  cudaError_t ce = cudaFuncSetAttribute(moe_tc_kernel<UP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (ce != cudaSuccess) return (int)ce;
+  const int N = UP ? a.F : a.W;
+  return gb_launch(moe_tc_kernel<UP, BM>, dim3((unsigned)tiles, (N + MT_BN - 1) / MT_BN), dim3(128), smem, s, a);
 }
 
 static int moe_check(const MoeArgs& a) {
@@ -400,11 +427,15 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
   if (sizeof(T) == 2 && a.W % 8 == 0 && a.F % 8 == 0 &&
       ((((uintptr_t)a.x) | ((uintptr_t)a.act) | ((uintptr_t)a.w_gate) | ((uintptr_t)a.w_up) |
         ((uintptr_t)a.w_down) | ((uintptr_t)a.out)) & 15) == 0) {
-    const long long tc_tiles = pairs / MT_BM + (pairs < a.E ? pairs : a.E);
-    if (tc_tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;
-    e = gb_launch(moe_tc_kernel<true>, dim3((unsigned)tc_tiles, (a.F + MT_BN - 1) / MT_BN), dim3(128), 0, s, a);
+    // few pairs per expert (a decode step): narrow tiles, deeper pipeline
+    if (pairs <= 4LL * a.E) {
+      e = moe_tc_launch<true, 16>(a, pairs, s);
+      if (e) return e;
+      return moe_tc_launch<false, 16>(a, pairs, s);
+    }
+    e = moe_tc_launch<true, 64>(a, pairs, s);
     if (e) return e;
-    return gb_launch(moe_tc_kernel<false>, dim3((unsigned)tc_tiles, (a.W + MT_BN - 1) / MT_BN), dim3(128), 0, s, a);
+    return moe_tc_launch<false, 64>(a, pairs, s);
   }
   const long long tiles = pairs / MOE_BM + (pairs < a.E ? pairs : a.E);
   if (tiles > 0x7fffffffLL) return GB_ERR_UNSUPPORTED;

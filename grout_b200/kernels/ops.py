@@ -1346,7 +1346,8 @@ class _DeltaArgs(ctypes.Structure):
     _fields_ = [("proj", _P), ("conv_w", _P), ("a_log", _P), ("dt_bias", _P), ("norm_w", _P),
                 ("token_seq", _P), ("cu_q", _P), ("slots", _P), ("state", _P), ("state_stride", _L),
                 ("prep", _P), ("o", _P), ("y", _P), ("n_tokens", _I), ("n_seqs", _I), ("H", _I),
-                ("G", _I), ("dk", _I), ("dv", _I), ("taps", _I), ("unit_eps", _F), ("norm_eps", _F)]
+                ("G", _I), ("dk", _I), ("dv", _I), ("taps", _I), ("unit_eps", _F), ("norm_eps", _F),
+                ("prep_stride", _I)]
 
 
 def delta_state_floats(H: int, G: int, dk: int, dv: int, taps: int) -> int:
@@ -1391,7 +1392,8 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     n_seqs = slots.shape[0]
     if token_seq.shape[0] != T or cu_q.shape[0] != n_seqs + 1:
         raise KernelError("token_seq, cu_q and slots do not describe the step's rows")
-    prep = torch.empty((T, Cc + 2 * H), dtype=torch.float32, device=proj.device)
+    prep_stride = (Cc + 2 * H + G + 3) // 4 * 4     # rows that start on 16 bytes
+    prep = torch.empty((T, prep_stride), dtype=torch.float32, device=proj.device)
     o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
     y = torch.empty((T, H * dv), dtype=dtype, device=proj.device)
     a = _DeltaArgs()
@@ -1401,7 +1403,7 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     a.state, a.state_stride = state.data_ptr(), state.stride(0)
     a.prep, a.o, a.y = prep.data_ptr(), o.data_ptr(), y.data_ptr()
     a.n_tokens, a.n_seqs, a.H, a.G, a.dk, a.dv, a.taps = T, n_seqs, H, G, dk, dv, taps
-    a.unit_eps, a.norm_eps = float(unit_eps), float(norm_eps)
+    a.unit_eps, a.norm_eps, a.prep_stride = float(unit_eps), float(norm_eps), prep_stride
     _check(_fn("delta", f"gb_delta_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "delta_forward", 4 if taps > 1 else 3)
     return y
