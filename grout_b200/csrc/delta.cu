@@ -11,23 +11,32 @@
 //
 // Everything here is 32-bit whatever the activation type: the one projection
 // that feeds it arrives as 32-bit sums, and only y, the o projection's input, is
-// rounded.  Four kernels:
+// rounded.  Five kernels:
 //
-//   prepare  one block per token: convolution (from the rows of this step and,
-//            for the first tokens of a continued sequence, from the kept tail),
-//            silu, unit vectors, beta, decay
+//   prepare  one block per token and kv head (its q and k) or run of value
+//            channels: convolution (from the rows of this step and, for the first
+//            tokens of a continued sequence, from the kept tail), silu, unit
+//            vectors, beta, decay
 //   keep     one block per sequence: the new tail of taps - 1 inputs
+//   gram     one block per group of 4 consecutive rows of a sequence and head: the
+//            products k_i . k_j (i < j) and k_i . q_j (i <= j) inside the group, and
+//            with them and the group's g and beta every scalar of the group that
+//            does not depend on the column
 //   scan     the recurrence.  The columns of S are independent recurrences, so a
-//            column is held in the registers of 8 lanes (dk / 8 elements each),
-//            16 columns a block, and a sequence's rows are walked in order.  A
-//            token's operands (its head's k and q, the block's 16 values, beta, g)
-//            reach shared memory 16 tokens at a time by asynchronous copies, two
-//            chunks in flight.  Per token both S^T k and S^T q are taken from the
-//            state as it stands, in one round of shuffles, and the read-out follows
-//            from them: o = g S^T q + u (k . q), since S' = g S + k u^T; the update
-//            of S is then off the path to the next token's sums.  A token's result
-//            does not depend on how the sequence was cut into steps: the order of
-//            operations is the same.
+//            column is held in the registers of 16 lanes (dk / 16 elements each),
+//            8 columns a block, and a sequence's rows are walked in order, four
+//            at a time: with c_j = g_1 .. g_j and s_0 the column before the group,
+//              s_{j-1} . k_j = c_{j-1} (s_0 . k_j) + sum_{i<j} (c_{j-1} / c_i) (k_i . k_j) u_i
+//              o_j = c_j (s_0 . q_j) + sum_{i<=j} (c_j / c_i) (k_i . q_j) u_i
+//              s_4 = c_4 s_0 + sum_i (c_4 / c_i) k_i u_i
+//            so the eight sums over dk that a group needs are taken from the column
+//            as it stands, in one round of shuffles, and what is sequential is a few
+//            operations on scalars (the quotients are products of the g between, never
+//            divisions).  The operands of 16 tokens at a time (their head's k and q,
+//            the block's 16 values, beta, g, the group's products) reach shared memory
+//            by asynchronous copies, two chunks in flight.  Groups are counted from the
+//            first row a step brings, so a sequence cut elsewhere gives the same
+//            result up to rounding, not bit for bit.
 //   finish   one warp per (token, head): norm over dv, weight, gate
 //
 // Columns of the projection: q [G dk] | k [G dk] | v [H dv] | gate [H dv] | b [H] | a [H].
@@ -47,68 +56,87 @@ struct DeltaArgs {
   const int* slots;        // [n_seqs]
   float* state;            // [slots, state_stride]
   long long state_stride;
-  float* prep;             // [n_tokens, prep_stride]: unit q | unit k | v | beta | decay | k . q [G]
+  float* prep;             // [n_tokens, prep_stride]: unit q | unit k | v | beta | decay | (pad to 4) |
+                           //   on a group's first row: its scalars [H, 48]
   float* o;                // [n_tokens, H, dv]
   void* y;                 // [n_tokens, H dv] in the activation type
   int n_tokens, n_seqs, H, G, dk, dv, taps;
   float unit_eps, norm_eps;
-  int prep_stride;         // floats between rows of prep: at least Cc + 2 H + G, a multiple of 4
+  int prep_stride;         // floats between rows of prep: round4(Cc + 2 H) + 48 H
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-__global__ void delta_prepare_kernel(const DeltaArgs a) {
-  extern __shared__ float row[];   // [Cc]
+// One block per (token, unit): unit g < G is kv head g's q and k together, the units after that are runs of
+// DELTA_PREP_V value channels; the block of unit 0 also takes beta and the decay.
+#define DELTA_PREP_V 256
+#define DELTA_MAX_TAPS 8     // taps fetched together; more are walked in turns
+
+__device__ __forceinline__ float delta_conv(const DeltaArgs& a, const float* tail, int t, int r,
+                                            int c, int Cc, int C_all) {
+  const int taps = a.taps;
+  float acc = 0.f;
+  for (int j0 = 0; j0 < taps; j0 += DELTA_MAX_TAPS) {
+    float x[DELTA_MAX_TAPS], w[DELTA_MAX_TAPS];
+#pragma unroll
+    for (int jj = 0; jj < DELTA_MAX_TAPS; ++jj) {      // all loads first: one trip to memory
+      const int j = j0 + jj, rr = r - j;               // the input j tokens back
+      x[jj] = 0.f, w[jj] = 0.f;
+      if (j < taps) {
+        w[jj] = a.conv_w[(size_t)c * taps + taps - 1 - j];
+        if (rr >= 0) x[jj] = a.proj[(size_t)(t - j) * C_all + c];
+        else if (tail) x[jj] = tail[(size_t)(taps - 1 + rr) * Cc + c];
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < DELTA_MAX_TAPS; ++jj) acc = fmaf(w[jj], x[jj], acc);
+  }
+  return silu_f(acc);
+}
+
+__global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaArgs a) {
+  extern __shared__ float row[];   // [2 dk]: a kv head's q and k after the convolution
+  __shared__ float scratch[32];
   pdl_launch_dependents_if_small();
-  pdl_wait();
-  const int t = blockIdx.x, tid = threadIdx.x;
-  const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, taps = a.taps;
+  const int t = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x;
+  const int H = a.H, G = a.G, dk = a.dk, dv = a.dv;
   const int Cc = 2 * G * dk + H * dv, C_all = Cc + H * dv + 2 * H, P = a.prep_stride;
   const int seq = a.token_seq[t];
   const int slot = a.slots[seq];
   const int r = t - a.cu_q[seq];                 // the token's place among its sequence's rows
   const float* tail = slot >= 0 ? a.state + (size_t)slot * a.state_stride : nullptr;
-  for (int c = tid; c < Cc; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {             // the input j tokens back
-      const int rr = r - j;
-      float x;
-      if (rr >= 0) x = a.proj[(size_t)(t - j) * C_all + c];
-      else x = tail ? tail[(size_t)(taps - 1 + rr) * Cc + c] : 0.f;
-      acc = fmaf(a.conv_w[(size_t)c * taps + taps - 1 - j], x, acc);
-    }
-    row[c] = silu_f(acc);
-  }
-  __syncthreads();
-  pdl_launch_dependents_if_large();
   float* out = a.prep + (size_t)t * P;
-  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-  const float mul = 1.0f / sqrtf((float)dk);
-  for (int head = warp; head < G; head += nwarps) {     // a kv head's q and k, and their product
-    const float* xq = row + head * dk;
-    const float* xk = row + (G + head) * dk;
-    float sq = 0.f, sk = 0.f;
-    for (int d = lane; d < dk; d += 32) sq += xq[d] * xq[d], sk += xk[d] * xk[d];
-    sq = warp_sum(sq), sk = warp_sum(sk);
-    const float iq = 1.0f / sqrtf(sq + a.unit_eps), ik = 1.0f / sqrtf(sk + a.unit_eps);
-    float kq = 0.f;
-    for (int d = lane; d < dk; d += 32) {
-      const float qv = xq[d] * iq * mul, kv = xk[d] * ik;
-      out[head * dk + d] = qv;
-      out[(G + head) * dk + d] = kv;
-      kq = fmaf(qv, kv, kq);
+  pdl_wait();
+  if (unit >= G) {                               // value channels: convolution and silu
+    const int c = 2 * G * dk + (unit - G) * DELTA_PREP_V + tid;
+    if (tid < DELTA_PREP_V && c < Cc) out[c] = delta_conv(a, tail, t, r, c, Cc, C_all);
+    return;
+  }
+  float sq = 0.f, sk = 0.f;
+  for (int i = tid; i < 2 * dk; i += blockDim.x) {
+    const int c = i < dk ? unit * dk + i : (G + unit) * dk + (i - dk);
+    const float v = delta_conv(a, tail, t, r, c, Cc, C_all);
+    row[i] = v;
+    if (i < dk) sq += v * v; else sk += v * v;
+  }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  const float iq = 1.0f / sqrtf(sq + a.unit_eps) * (1.0f / sqrtf((float)dk));
+  const float ik = 1.0f / sqrtf(sk + a.unit_eps);
+  for (int d = tid; d < dk; d += blockDim.x) {
+    out[unit * dk + d] = row[d] * iq;
+    out[(G + unit) * dk + d] = row[dk + d] * ik;
+  }
+  if (unit == 0) {
+    for (int h = tid; h < H; h += blockDim.x) {
+      const float b = a.proj[(size_t)t * C_all + Cc + H * dv + h];
+      const float al = a.proj[(size_t)t * C_all + Cc + H * dv + H + h];
+      out[Cc + h] = 1.0f / (1.0f + expf(-b));
+      out[Cc + H + h] = expf(-expf(a.a_log[h]) * softplus_f(al + a.dt_bias[h]));
     }
-    kq = warp_sum(kq);
-    if (lane == 0) out[Cc + 2 * H + head] = kq;
   }
-  for (int c = 2 * G * dk + tid; c < Cc; c += blockDim.x) out[c] = row[c];
-  for (int h = tid; h < H; h += blockDim.x) {
-    const float b = a.proj[(size_t)t * C_all + Cc + H * dv + h];
-    const float al = a.proj[(size_t)t * C_all + Cc + H * dv + H + h];
-    out[Cc + h] = 1.0f / (1.0f + expf(-b));
-    out[Cc + H + h] = expf(-expf(a.a_log[h]) * softplus_f(al + a.dt_bias[h]));
-  }
+  pdl_launch_dependents_if_large();
 }
 
 __global__ void delta_keep_kernel(const DeltaArgs a) {
@@ -131,9 +159,71 @@ __global__ void delta_keep_kernel(const DeltaArgs a) {
   }
 }
 
-#define DELTA_LANES 8       // lanes that share a column of S
-#define DELTA_COLS 16       // columns of S per block
+#define DELTA_LANES 16      // lanes that share a column of S
+#define DELTA_COLS 8        // columns of S per block
 #define DELTA_TT 16         // tokens whose operands are staged together
+#define DELTA_B 4           // rows of a group
+
+__host__ __device__ __forceinline__ int delta_gram_offset(int Cc, int H) { return (Cc + 2 * H + 3) / 4 * 4; }
+
+// The scalars of a group of DELTA_B rows and one head that do not depend on the column
+// (c_j = g_1 .. g_j, c_0 = 1; quotients c_j / c_i are products of the g between):
+//   [0, 4)   A_j  = beta_j g_j c_{j-1}                       u_j = beta_j v_j - A_j (s_0 . k_j)
+//   [4, 20)  C_ij = beta_j g_j (c_{j-1} / c_i) (k_i . k_j)          - sum_{i<j} C_ij u_i
+//   [20, 24) c_j                                              o_j = c_j (s_0 . q_j)
+//   [24, 40) D_ij = (c_j / c_i) (k_i . q_j)                         + sum_{i<=j} D_ij u_i
+//   [40, 44) E_i  = c_4 / c_i                                 s_4 = c_4 s_0 + sum_i E_i u_i k_i
+//   [44, 48) beta_j
+// Rows beyond the sequence's end are neutral (beta 0, g 1, products 0).
+#define DELTA_COEF 48
+__global__ void __launch_bounds__(128) delta_gram_kernel(const DeltaArgs a) {
+  __shared__ float dots[2 * DELTA_B * DELTA_B];
+  pdl_launch_dependents_if_small();
+  constexpr int B = DELTA_B;
+  const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.G, H = a.H, dk = a.dk, P = a.prep_stride;
+  const int Cc = 2 * G * dk + H * a.dv, kvh = h / (H / G);
+  const int seq = a.token_seq[t];
+  const int row0 = a.cu_q[seq], r = t - row0;
+  if (r % B) return;
+  const int nb = min(B, a.cu_q[seq + 1] - t);
+  pdl_wait();
+  for (int e = warp; e < 2 * B * B; e += 4) {       // e < 16: k_i . k_j, else k_i . q_j
+    const int with_q = e / (B * B), i = (e % (B * B)) / B, j = e % B;
+    float acc = 0.f;
+    if (i < nb && j < nb && (with_q ? i <= j : i < j)) {
+      const float* ki = a.prep + (size_t)(t + i) * P + (G + kvh) * dk;
+      const float* xj = a.prep + (size_t)(t + j) * P + (with_q ? kvh : G + kvh) * dk;
+      for (int d = lane; d < dk; d += 32) acc = fmaf(ki[d], xj[d], acc);
+      acc = warp_sum(acc);
+    }
+    if (lane == 0) dots[e] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float* out = a.prep + (size_t)t * P + delta_gram_offset(Cc, H) + h * DELTA_COEF;
+    float beta[B], g[B], quot[B][B], cum[B + 1];
+    cum[0] = 1.f;
+    for (int j = 0; j < B; ++j) {
+      beta[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + h] : 0.f;
+      g[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + H + h] : 1.f;
+      cum[j + 1] = cum[j] * g[j];
+      quot[j][j] = 1.f;
+      for (int i = 0; i < j; ++i) quot[i][j] = quot[i][j - 1] * g[j];
+    }
+    for (int j = 0; j < B; ++j) {
+      out[j] = beta[j] * g[j] * cum[j];
+      out[20 + j] = cum[j + 1];
+      out[40 + j] = quot[j][B - 1];
+      out[44 + j] = beta[j];
+      for (int i = 0; i < B; ++i) {
+        out[4 + i * B + j] = i < j ? beta[j] * g[j] * quot[i][j - 1] * dots[i * B + j] : 0.f;
+        out[24 + i * B + j] = i <= j ? quot[i][j] * dots[B * B + i * B + j] : 0.f;
+      }
+    }
+  }
+  pdl_launch_dependents_if_large();
+}
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -141,23 +231,26 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 }
 
 // R floats of a column per lane, in pieces of four: piece i of lane l holds the
-// elements (i * 8 + l) * 4 .. + 3, so that the eight lanes of a column read 128
-// contiguous bytes of shared memory, and of the state, at a time.
+// elements (i * 16 + l) * 4 .. + 3, so that the lanes of a column read contiguous
+// bytes of shared memory, and of the state, at a time.
 template <int R>
 __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(const DeltaArgs a) {
   extern __shared__ __align__(16) float sm[];
+  constexpr int B = DELTA_B;
   constexpr int DKP = DELTA_LANES * R;                       // dk filled up with zeros
-  constexpr int STAGE = DELTA_TT * (2 * DKP + DELTA_COLS + 4);   // q | k | v | beta, g, k.q, -
+  constexpr int GRAM = DELTA_COEF;
+  // q | k | v | the groups' scalars
+  constexpr int STAGE = DELTA_TT * (2 * DKP + DELTA_COLS) + (DELTA_TT / B) * GRAM;
   pdl_launch_dependents_if_small();
   const int seq = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
   const int col0 = blockIdx.x * DELTA_COLS;
   const int col = col0 + tid / DELTA_LANES, l = tid % DELTA_LANES;
   const int H = a.H, G = a.G, dk = a.dk, dv = a.dv;
   const int Cc = 2 * G * dk + H * dv, P = a.prep_stride;
+  const int gram_off = delta_gram_offset(Cc, H);
   const int kvh = h / (H / G);
   const bool active = col < dv;
-  if (dk < DKP)
-    for (int i = tid; i < 2 * STAGE; i += blockDim.x) sm[i] = 0.f;   // what no copy writes stays zero
+  for (int i = tid; i < 2 * STAGE; i += blockDim.x) sm[i] = 0.f;   // what no copy writes stays zero
   pdl_wait();
   const int row0 = a.cu_q[seq], n = a.cu_q[seq + 1] - row0;
   if (n <= 0) return;
@@ -174,36 +267,40 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     S[i] = sp && e < dk ? sp[e] : 0.f;
   }
   const bool wide = (dk & 3) == 0;     // 16-byte copies; prep rows are 16-byte aligned
+  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   auto stage_in = [&](int chunk, int st) {
     float* base = sm + st * STAGE;
+    float* vs = base + 2 * DELTA_TT * DKP;
+    float* gr = vs + DELTA_TT * DELTA_COLS;
     const int t0 = row0 + chunk * DELTA_TT;
     const int nt = min(DELTA_TT, row0 + n - t0);
-    if (wide) {
-      const int per = dk >> 2;                              // pieces of a token's q (or k)
-      for (int i = tid; i < nt * 2 * per; i += blockDim.x) {
-        const int tt = i / (2 * per), r = i % (2 * per), which = r / per, pc = r % per;
-        const float* src = a.prep + (size_t)(t0 + tt) * P + (which * G + kvh) * dk + pc * 4;
-        cp_async16(base + (which * DELTA_TT + tt) * DKP + pc * 4, src, true);
+    for (int tt = warp; tt < nt; tt += nwarps) {          // a warp per token: its q, its k, its values
+      const float* src = a.prep + (size_t)(t0 + tt) * P;
+      if (wide) {
+        for (int pc = lane; pc < dk / 4; pc += 32) {
+          cp_async16(base + tt * DKP + pc * 4, src + kvh * dk + pc * 4, true);
+          cp_async16(base + (DELTA_TT + tt) * DKP + pc * 4, src + (G + kvh) * dk + pc * 4, true);
+        }
+      } else {
+        for (int d = lane; d < dk; d += 32) {
+          cp_async4(base + tt * DKP + d, src + kvh * dk + d);
+          cp_async4(base + (DELTA_TT + tt) * DKP + d, src + (G + kvh) * dk + d);
+        }
       }
-    } else {
-      for (int i = tid; i < nt * 2 * dk; i += blockDim.x) {
-        const int tt = i / (2 * dk), r = i % (2 * dk), which = r / dk, d = r % dk;
-        cp_async4(base + (which * DELTA_TT + tt) * DKP + d,
-                  a.prep + (size_t)(t0 + tt) * P + (which * G + kvh) * dk + d);
-      }
+      if (lane < DELTA_COLS && col0 + lane < dv)
+        cp_async4(vs + tt * DELTA_COLS + lane, src + 2 * G * dk + h * dv + col0 + lane);
     }
-    float* vs = base + 2 * DELTA_TT * DKP;
-    float* sc = vs + DELTA_TT * DELTA_COLS;
-    for (int i = tid; i < nt * DELTA_COLS; i += blockDim.x) {
-      const int tt = i / DELTA_COLS, c = i % DELTA_COLS;
-      if (col0 + c < dv) cp_async4(vs + i, a.prep + (size_t)(t0 + tt) * P + 2 * G * dk + h * dv + col0 + c);
-    }
-    for (int i = tid; i < nt * 3; i += blockDim.x) {
-      const int tt = i / 3, w = i % 3;
-      const int off = w == 0 ? Cc + h : (w == 1 ? Cc + H + h : Cc + 2 * H + kvh);
-      cp_async4(sc + tt * 4 + w, a.prep + (size_t)(t0 + tt) * P + off);
-    }
+    for (int gi = warp; gi * B < nt; gi += nwarps)        // a warp per group: its scalars
+      for (int e = lane; e < GRAM / 4; e += 32)
+        cp_async16(gr + gi * GRAM + e * 4, a.prep + (size_t)(t0 + gi * B) * P + gram_off + h * GRAM + e * 4, true);
     cp_async_commit();
+    if (nt < DELTA_TT) {   // the sequence ends inside this chunk: rows beyond it are zeros
+      for (int i = tid; i < (DELTA_TT - nt) * DKP; i += blockDim.x) {
+        base[nt * DKP + i] = 0.f;
+        base[(DELTA_TT + nt) * DKP + i] = 0.f;
+      }
+      for (int i = tid; i < (DELTA_TT - nt) * DELTA_COLS; i += blockDim.x) vs[nt * DELTA_COLS + i] = 0.f;
+    }
   };
   const int n_chunks = (n + DELTA_TT - 1) / DELTA_TT;
   stage_in(0, 0);
@@ -218,35 +315,65 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     __syncthreads();
     const float* base = sm + st * STAGE;
     const float* vs = base + 2 * DELTA_TT * DKP;
-    const float* sc = vs + DELTA_TT * DELTA_COLS;
+    const float* gr = vs + DELTA_TT * DELTA_COLS;
     const int t0 = row0 + c * DELTA_TT;
     const int nt = min(DELTA_TT, row0 + n - t0);
-    for (int tt = 0; tt < nt; ++tt) {
-      const float4* qp = reinterpret_cast<const float4*>(base + tt * DKP) + l;
-      const float4* kp = reinterpret_cast<const float4*>(base + (DELTA_TT + tt) * DKP) + l;
-      float k[R];
-      float d1[4] = {0.f, 0.f, 0.f, 0.f}, d2[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g0 = 0; g0 < nt; g0 += B) {
+      float k[B][R], sk[B], sq[B];
 #pragma unroll
-      for (int i = 0; i < R / 4; ++i) {
-        const float4 kk = kp[i * DELTA_LANES], qq = qp[i * DELTA_LANES];
-        k[4 * i] = kk.x, k[4 * i + 1] = kk.y, k[4 * i + 2] = kk.z, k[4 * i + 3] = kk.w;
-        d1[0] = fmaf(S[4 * i], kk.x, d1[0]), d1[1] = fmaf(S[4 * i + 1], kk.y, d1[1]);
-        d1[2] = fmaf(S[4 * i + 2], kk.z, d1[2]), d1[3] = fmaf(S[4 * i + 3], kk.w, d1[3]);
-        d2[0] = fmaf(S[4 * i], qq.x, d2[0]), d2[1] = fmaf(S[4 * i + 1], qq.y, d2[1]);
-        d2[2] = fmaf(S[4 * i + 2], qq.z, d2[2]), d2[3] = fmaf(S[4 * i + 3], qq.w, d2[3]);
+      for (int j = 0; j < B; ++j) {
+        const float4* qp = reinterpret_cast<const float4*>(base + (g0 + j) * DKP) + l;
+        const float4* kp = reinterpret_cast<const float4*>(base + (DELTA_TT + g0 + j) * DKP) + l;
+        float d1 = 0.f, d2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i) {
+          const float4 kk = kp[i * DELTA_LANES], qq = qp[i * DELTA_LANES];
+          k[j][4 * i] = kk.x, k[j][4 * i + 1] = kk.y, k[j][4 * i + 2] = kk.z, k[j][4 * i + 3] = kk.w;
+          d1 = fmaf(S[4 * i], kk.x, d1), d1 = fmaf(S[4 * i + 1], kk.y, d1);
+          d1 = fmaf(S[4 * i + 2], kk.z, d1), d1 = fmaf(S[4 * i + 3], kk.w, d1);
+          d2 = fmaf(S[4 * i], qq.x, d2), d2 = fmaf(S[4 * i + 1], qq.y, d2);
+          d2 = fmaf(S[4 * i + 2], qq.z, d2), d2 = fmaf(S[4 * i + 3], qq.w, d2);
+        }
+        sk[j] = d1, sq[j] = d2;
       }
-      float sk = (d1[0] + d1[1]) + (d1[2] + d1[3]), sq = (d2[0] + d2[1]) + (d2[2] + d2[3]);
 #pragma unroll
-      for (int m = 1; m < DELTA_LANES; m <<= 1) {
-        sk += __shfl_xor_sync(0xffffffffu, sk, m);
-        sq += __shfl_xor_sync(0xffffffffu, sq, m);
+      for (int m = 1; m < DELTA_LANES; m <<= 1)
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+          sk[j] += __shfl_xor_sync(0xffffffffu, sk[j], m);
+          sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], m);
+        }
+      // what is left of the group's scalars depends on the column: every lane computes the same
+      const float4* cf = reinterpret_cast<const float4*>(gr + (g0 / B) * GRAM);
+      float co[GRAM];
+#pragma unroll
+      for (int i = 0; i < GRAM / 4; ++i) {
+        const float4 x = cf[i];
+        co[4 * i] = x.x, co[4 * i + 1] = x.y, co[4 * i + 2] = x.z, co[4 * i + 3] = x.w;
       }
-      const float beta = sc[tt * 4], g = sc[tt * 4 + 1], kq = sc[tt * 4 + 2];
-      const float v = vs[tt * DELTA_COLS + (tid / DELTA_LANES)];
-      const float u = beta * (v - g * sk);
+      float u[B], w[B];
 #pragma unroll
-      for (int i = 0; i < R; ++i) S[i] = fmaf(k[i], u, g * S[i]);
-      if (l == 0 && active) a.o[((size_t)(t0 + tt) * H + h) * dv + col] = fmaf(u, kq, g * sq);
+      for (int j = 0; j < B; ++j) {
+        const float v = vs[(g0 + j) * DELTA_COLS + (tid / DELTA_LANES)];
+        float uj = fmaf(co[44 + j], v, -co[j] * sk[j]);
+#pragma unroll
+        for (int i = 0; i < j; ++i) uj = fmaf(-co[4 + i * B + j], u[i], uj);
+        u[j] = uj;
+        float o = co[20 + j] * sq[j];
+#pragma unroll
+        for (int i = 0; i <= j; ++i) o = fmaf(co[24 + i * B + j], u[i], o);
+        if (l == 0 && active && g0 + j < nt) a.o[((size_t)(t0 + g0 + j) * H + h) * dv + col] = o;
+      }
+#pragma unroll
+      for (int i = 0; i < B; ++i) w[i] = co[40 + i] * u[i];
+      const float cum = co[20 + B - 1];
+#pragma unroll
+      for (int x = 0; x < R; ++x) {
+        float sx = cum * S[x];
+#pragma unroll
+        for (int i = 0; i < B; ++i) sx = fmaf(k[i][x], w[i], sx);
+        S[x] = sx;
+      }
     }
     __syncthreads();   // the stage is refilled by the next turn's copies
   }
@@ -284,7 +411,8 @@ __global__ void delta_finish_kernel(const DeltaArgs a) {
 template <int R>
 static int scan_launch(const DeltaArgs& a, cudaStream_t s) {
   const dim3 grid((a.dv + DELTA_COLS - 1) / DELTA_COLS, a.H, a.n_seqs), block(DELTA_LANES * DELTA_COLS);
-  const size_t smem = (size_t)2 * DELTA_TT * (2 * DELTA_LANES * R + DELTA_COLS + 4) * sizeof(float);
+  const size_t smem = (size_t)2 * (DELTA_TT * (2 * DELTA_LANES * R + DELTA_COLS) +
+                                   (DELTA_TT / DELTA_B) * DELTA_COEF) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t ce = cudaFuncSetAttribute(delta_scan_kernel<R>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -297,8 +425,9 @@ static int delta_check(const DeltaArgs& a) {
   if (a.n_tokens < 0 || a.n_seqs <= 0 || a.H <= 0 || a.G <= 0 || a.H % a.G || a.dk <= 0 ||
       a.dv <= 0 || a.taps <= 0 || !a.proj || !a.state || !a.prep || !a.o || !a.y)
     return GB_ERR_BAD_ARG;
-  if (a.dk > 32 * DELTA_LANES) return GB_ERR_UNSUPPORTED;
-  if (a.prep_stride < 2 * a.G * a.dk + a.H * a.dv + 2 * a.H + a.G || (a.prep_stride & 3) ||
+  if (a.dk > 16 * DELTA_LANES) return GB_ERR_UNSUPPORTED;
+  const int Cc = 2 * a.G * a.dk + a.H * a.dv;
+  if (a.prep_stride != delta_gram_offset(Cc, a.H) + DELTA_COEF * a.H ||
       (((uintptr_t)a.prep) & 15))
     return GB_ERR_BAD_ARG;
   return 0;
@@ -310,32 +439,27 @@ static int delta_forward(const DeltaArgs& a, cudaStream_t s) {
   if (e) return e;
   if (a.n_tokens == 0) return 0;
   const int Cc = 2 * a.G * a.dk + a.H * a.dv;
-  const size_t smem = (size_t)Cc * sizeof(float);
-  if (smem > 200 * 1024) return GB_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024) {
-    cudaError_t ce = cudaFuncSetAttribute(delta_prepare_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (ce != cudaSuccess) return (int)ce;
-  }
-  e = gb_launch(delta_prepare_kernel, dim3(a.n_tokens), dim3(256), smem, s, a);
+  const int units = a.G + (a.H * a.dv + DELTA_PREP_V - 1) / DELTA_PREP_V;
+  e = gb_launch(delta_prepare_kernel, dim3(a.n_tokens, units), dim3(256),
+                (size_t)2 * a.dk * sizeof(float), s, a);
   if (e) return e;
   if (a.taps > 1) {
     e = gb_launch(delta_keep_kernel, dim3(a.n_seqs, (Cc + 1023) / 1024), dim3(256), 0, s, a);
     if (e) return e;
   }
+  e = gb_launch(delta_gram_kernel, dim3(a.n_tokens, a.H), dim3(128), 0, s, a);
+  if (e) return e;
   const int per_lane = (a.dk + DELTA_LANES - 1) / DELTA_LANES;
   if (per_lane <= 4) e = scan_launch<4>(a, s);
   else if (per_lane <= 8) e = scan_launch<8>(a, s);
   else if (per_lane <= 12) e = scan_launch<12>(a, s);
-  else if (per_lane <= 16) e = scan_launch<16>(a, s);
-  else if (per_lane <= 24) e = scan_launch<24>(a, s);
-  else e = scan_launch<32>(a, s);
+  else e = scan_launch<16>(a, s);
   if (e) return e;
   const int warps = a.H < 8 ? a.H : 8;
   return gb_launch(delta_finish_kernel<T>, dim3(a.n_tokens, (a.H + warps - 1) / warps),
                    dim3(warps * 32), 0, s, a);
 }
 
-// Four launches: prepare, keep (with more than one tap), scan, finish.
+// Five launches: prepare, keep (with more than one tap), gram, scan, finish.
 GB_EXPORT int gb_delta_forward_f32(const DeltaArgs* a, cudaStream_t s) { return delta_forward<float>(*a, s); }
 GB_EXPORT int gb_delta_forward_bf16(const DeltaArgs* a, cudaStream_t s) { return delta_forward<bf16>(*a, s); }

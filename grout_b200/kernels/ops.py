@@ -1392,7 +1392,9 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     n_seqs = slots.shape[0]
     if token_seq.shape[0] != T or cu_q.shape[0] != n_seqs + 1:
         raise KernelError("token_seq, cu_q and slots do not describe the step's rows")
-    prep_stride = (Cc + 2 * H + G + 3) // 4 * 4     # rows that start on 16 bytes
+    # rows that start on 16 bytes; behind a row's own values, room for the scalars of the
+    # group of four rows that it opens
+    prep_stride = (Cc + 2 * H + 3) // 4 * 4 + 48 * H
     prep = torch.empty((T, prep_stride), dtype=torch.float32, device=proj.device)
     o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
     y = torch.empty((T, H * dv), dtype=dtype, device=proj.device)
@@ -1405,7 +1407,7 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     a.n_tokens, a.n_seqs, a.H, a.G, a.dk, a.dv, a.taps = T, n_seqs, H, G, dk, dv, taps
     a.unit_eps, a.norm_eps, a.prep_stride = float(unit_eps), float(norm_eps), prep_stride
     _check(_fn("delta", f"gb_delta_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "delta_forward", 4 if taps > 1 else 3)
+           "delta_forward", 5 if taps > 1 else 4)
     return y
 
 

@@ -141,8 +141,9 @@ def test_delta_rule_whole_in_portions_and_token_by_token(m):
     close(whole, want, torch.float32, "whole")
     for cuts in ([2] * 75, [1] * T, [1, 2, 3, 100, 44], [149, 1]):
         got, _ = _delta_run(w, m, xs, cuts, torch.float32)
-        # the recurrence is walked in the same order however the rows are cut
-        assert torch.equal(got, whole), cuts
+        # the same recurrence however the rows are cut (rows are walked in groups that
+        # start where a step starts, so the rounding differs)
+        assert float((got - whole).abs().max()) < 1e-5, cuts
     half, _ = _delta_run(w, m, xs, [T], torch.bfloat16)
     close(half, want, torch.bfloat16, "bfloat16 output")
 
@@ -169,15 +170,16 @@ def test_delta_rule_batches_slots_used_again_and_padding():
     # a in slot 2 and b in slot 1 start together with a padding sequence between them
     s1 = Step([(2, 0, 30), (-1, 0, 3), (1, 0, 8)]).ctx
     y = run(s1, torch.cat([xa[:30], rnd(3, W, seed=8), xb[:8]]))
-    assert torch.equal(y[:30], alone_a[:30]) and torch.equal(y[33:], alone_b[:8])
+    same = lambda p, q: float((p - q).abs().max()) < 1e-5
+    assert same(y[:30], alone_a[:30]) and same(y[33:], alone_b[:8])
     assert float(state[3].abs().max()) == 0.0                         # padding rows store nothing
     s2 = Step([(1, 8, 1), (2, 30, 1)]).ctx                            # then decoded together, other order
     y = run(s2, torch.cat([xb[8:9], xa[30:31]]))
-    assert torch.equal(y[0], alone_b[8]) and torch.equal(y[1], alone_a[30])
+    assert same(y[0], alone_b[8]) and same(y[1], alone_a[30])
     state[1].zero_()                                                  # b ends; its slot serves a new request
     s3 = Step([(2, 31, 9), (1, 0, 9)]).ctx
     y = run(s3, torch.cat([xa[31:], xb]))
-    assert torch.equal(y[:9], alone_a[31:]) and torch.equal(y[9:], alone_b)
+    assert same(y[:9], alone_a[31:]) and same(y[9:], alone_b)
 
 
 def test_delta_rule_reads_a_far_key():
