@@ -11,13 +11,12 @@
 //
 // Everything here is 32-bit whatever the activation type: the one projection
 // that feeds it arrives as 32-bit sums, and only y, the o projection's input, is
-// rounded.  Five kernels:
+// rounded.  Four kernels:
 //
 //   prepare  one block per token and kv head (its q and k) or run of value
 //            channels: convolution (from the rows of this step and, for the first
 //            tokens of a continued sequence, from the kept tail), silu, unit
 //            vectors, beta, decay
-//   keep     one block per sequence: the new tail of taps - 1 inputs
 //   gram     one block per group of 4 consecutive rows of a sequence and head: the
 //            products k_i . k_j (i < j) and k_i . q_j (i <= j) inside the group, and
 //            with them and the group's g and beta every scalar of the group that
@@ -37,7 +36,8 @@
 //            by asynchronous copies, two chunks in flight.  Groups are counted from the
 //            first row a step brings, so a sequence cut elsewhere gives the same
 //            result up to rounding, not bit for bit.
-//   finish   one warp per (token, head): norm over dv, weight, gate
+//   finish   one warp per (token, head): norm over dv, weight, gate; the block of a
+//            sequence's first row then keeps the new tail of taps - 1 inputs
 //
 // Columns of the projection: q [G dk] | k [G dk] | v [H dv] | gate [H dv] | b [H] | a [H].
 // A sequence's state is one row of floats: the tail [taps - 1, Cc] (Cc = the
@@ -63,6 +63,8 @@ struct DeltaArgs {
   int n_tokens, n_seqs, H, G, dk, dv, taps;
   float unit_eps, norm_eps;
   int prep_stride;         // floats between rows of prep: round4(Cc + 2 H) + 48 H
+  int few_rows;            // no sequence brings more than DELTA_B rows (a decode step): the scan
+                           //   works out its one group's scalars itself and `gram` is not launched
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -139,22 +141,31 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaArgs a) {
   pdl_launch_dependents_if_large();
 }
 
-__global__ void delta_keep_kernel(const DeltaArgs a) {
-  pdl_wait();
-  const int seq = blockIdx.x;
+// The new tail of a sequence: the last taps - 1 inputs of its convolutions.  Entry s
+// holds the input at n - (taps - 1) + s rows from the step's first; an entry that stays
+// is read (at n + s > s) before anything at or above it is written.
+__device__ __forceinline__ void delta_keep_tail(const DeltaArgs& a, int seq) {
   const int slot = a.slots[seq];
   const int row0 = a.cu_q[seq], n = a.cu_q[seq + 1] - row0;
   if (slot < 0 || n <= 0) return;
   const int taps = a.taps;
   const int Cc = 2 * a.G * a.dk + a.H * a.dv, C_all = Cc + a.H * a.dv + 2 * a.H;
   float* tail = a.state + (size_t)slot * a.state_stride;
+  // the blocks of the row (blockIdx.y) share the channels; up to eight entries are read
+  // together before any of them is written
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < Cc; c += gridDim.y * blockDim.x) {
-    // entry s holds the input at n - (taps - 1) + s rows from the step's first; an
-    // entry that stays is read (at n + s > s) before anything at or above it is written
-    for (int s = 0; s < taps - 1; ++s) {
-      const int rr = n - (taps - 1) + s;
-      tail[(size_t)s * Cc + c] = rr >= 0 ? a.proj[(size_t)(row0 + rr) * C_all + c]
-                                         : tail[(size_t)(taps - 1 + rr) * Cc + c];
+    for (int s0 = 0; s0 < taps - 1; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int s = s0 + u, rr = n - (taps - 1) + s;
+        v[u] = 0.f;
+        if (s < taps - 1)
+          v[u] = rr >= 0 ? a.proj[(size_t)(row0 + rr) * C_all + c] : tail[(size_t)(taps - 1 + rr) * Cc + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < taps - 1) tail[(size_t)(s0 + u) * Cc + c] = v[u];
     }
   }
 }
@@ -176,6 +187,29 @@ __host__ __device__ __forceinline__ int delta_gram_offset(int Cc, int H) { retur
 //   [44, 48) beta_j
 // Rows beyond the sequence's end are neutral (beta 0, g 1, products 0).
 #define DELTA_COEF 48
+__device__ __forceinline__ void delta_group_scalars(float* out, const float* dots,
+                                                    const float (&beta)[DELTA_B],
+                                                    const float (&g)[DELTA_B]) {
+  constexpr int B = DELTA_B;
+  float quot[B][B], cum[B + 1];
+  cum[0] = 1.f;
+  for (int j = 0; j < B; ++j) {
+    cum[j + 1] = cum[j] * g[j];
+    quot[j][j] = 1.f;
+    for (int i = 0; i < j; ++i) quot[i][j] = quot[i][j - 1] * g[j];
+  }
+  for (int j = 0; j < B; ++j) {
+    out[j] = beta[j] * g[j] * cum[j];
+    out[20 + j] = cum[j + 1];
+    out[40 + j] = quot[j][B - 1];
+    out[44 + j] = beta[j];
+    for (int i = 0; i < B; ++i) {
+      out[4 + i * B + j] = i < j ? beta[j] * g[j] * quot[i][j - 1] * dots[i * B + j] : 0.f;
+      out[24 + i * B + j] = i <= j ? quot[i][j] * dots[B * B + i * B + j] : 0.f;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) delta_gram_kernel(const DeltaArgs a) {
   __shared__ float dots[2 * DELTA_B * DELTA_B];
   pdl_launch_dependents_if_small();
@@ -201,26 +235,12 @@ __global__ void __launch_bounds__(128) delta_gram_kernel(const DeltaArgs a) {
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    float* out = a.prep + (size_t)t * P + delta_gram_offset(Cc, H) + h * DELTA_COEF;
-    float beta[B], g[B], quot[B][B], cum[B + 1];
-    cum[0] = 1.f;
+    float beta[B], g[B];
     for (int j = 0; j < B; ++j) {
       beta[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + h] : 0.f;
       g[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + H + h] : 1.f;
-      cum[j + 1] = cum[j] * g[j];
-      quot[j][j] = 1.f;
-      for (int i = 0; i < j; ++i) quot[i][j] = quot[i][j - 1] * g[j];
     }
-    for (int j = 0; j < B; ++j) {
-      out[j] = beta[j] * g[j] * cum[j];
-      out[20 + j] = cum[j + 1];
-      out[40 + j] = quot[j][B - 1];
-      out[44 + j] = beta[j];
-      for (int i = 0; i < B; ++i) {
-        out[4 + i * B + j] = i < j ? beta[j] * g[j] * quot[i][j - 1] * dots[i * B + j] : 0.f;
-        out[24 + i * B + j] = i <= j ? quot[i][j] * dots[B * B + i * B + j] : 0.f;
-      }
-    }
+    delta_group_scalars(a.prep + (size_t)t * P + delta_gram_offset(Cc, H) + h * DELTA_COEF, dots, beta, g);
   }
   pdl_launch_dependents_if_large();
 }
@@ -250,7 +270,8 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
   const int gram_off = delta_gram_offset(Cc, H);
   const int kvh = h / (H / G);
   const bool active = col < dv;
-  for (int i = tid; i < 2 * STAGE; i += blockDim.x) sm[i] = 0.f;   // what no copy writes stays zero
+  if (dk < DKP)
+    for (int i = tid; i < 2 * STAGE; i += blockDim.x) sm[i] = 0.f;   // what no copy writes stays zero
   pdl_wait();
   const int row0 = a.cu_q[seq], n = a.cu_q[seq + 1] - row0;
   if (n <= 0) return;
@@ -260,13 +281,20 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
                   ? a.state + (size_t)slot * a.state_stride + (size_t)(a.taps - 1) * Cc +
                         ((size_t)h * dv + col) * dk
                   : nullptr;
+  const bool wide = (dk & 3) == 0;     // 16-byte copies; prep rows are 16-byte aligned
+  const bool wide_state = wide && sp && (((uintptr_t)sp) & 15) == 0;
   float S[R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int e = ((i >> 2) * DELTA_LANES + l) * 4 + (i & 3);
-    S[i] = sp && e < dk ? sp[e] : 0.f;
+  for (int i = 0; i < R / 4; ++i) {
+    const int e = (i * DELTA_LANES + l) * 4;
+    if (wide_state) {
+      const float4 x = e < dk ? *reinterpret_cast<const float4*>(sp + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[4 * i] = x.x, S[4 * i + 1] = x.y, S[4 * i + 2] = x.z, S[4 * i + 3] = x.w;
+    } else {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) S[4 * i + x] = sp && e + x < dk ? sp[e + x] : 0.f;
+    }
   }
-  const bool wide = (dk & 3) == 0;     // 16-byte copies; prep rows are 16-byte aligned
   const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   auto stage_in = [&](int chunk, int st) {
     float* base = sm + st * STAGE;
@@ -290,16 +318,18 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
       if (lane < DELTA_COLS && col0 + lane < dv)
         cp_async4(vs + tt * DELTA_COLS + lane, src + 2 * G * dk + h * dv + col0 + lane);
     }
-    for (int gi = warp; gi * B < nt; gi += nwarps)        // a warp per group: its scalars
-      for (int e = lane; e < GRAM / 4; e += 32)
-        cp_async16(gr + gi * GRAM + e * 4, a.prep + (size_t)(t0 + gi * B) * P + gram_off + h * GRAM + e * 4, true);
+    if (!a.few_rows)
+      for (int gi = warp; gi * B < nt; gi += nwarps)      // a warp per group: its scalars
+        for (int e = lane; e < GRAM / 4; e += 32)
+          cp_async16(gr + gi * GRAM + e * 4, a.prep + (size_t)(t0 + gi * B) * P + gram_off + h * GRAM + e * 4, true);
     cp_async_commit();
-    if (nt < DELTA_TT) {   // the sequence ends inside this chunk: rows beyond it are zeros
-      for (int i = tid; i < (DELTA_TT - nt) * DKP; i += blockDim.x) {
+    const int fill = ((nt + B - 1) / B) * B - nt;   // the sequence ends inside a group: its other rows are zeros
+    if (fill > 0) {
+      for (int i = tid; i < fill * DKP; i += blockDim.x) {
         base[nt * DKP + i] = 0.f;
         base[(DELTA_TT + nt) * DKP + i] = 0.f;
       }
-      for (int i = tid; i < (DELTA_TT - nt) * DELTA_COLS; i += blockDim.x) vs[nt * DELTA_COLS + i] = 0.f;
+      for (int i = tid; i < fill * DELTA_COLS; i += blockDim.x) vs[nt * DELTA_COLS + i] = 0.f;
     }
   };
   const int n_chunks = (n + DELTA_TT - 1) / DELTA_TT;
@@ -318,6 +348,30 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     const float* gr = vs + DELTA_TT * DELTA_COLS;
     const int t0 = row0 + c * DELTA_TT;
     const int nt = min(DELTA_TT, row0 + n - t0);
+    if (a.few_rows) {       // the one group's products from the staged rows, then its scalars
+      __shared__ float dots[2 * DELTA_B * DELTA_B];
+      for (int e = warp; e < 2 * B * B; e += nwarps) {
+        const int with_q = e / (B * B), i = (e % (B * B)) / B, j = e % B;
+        float acc = 0.f;
+        if (i < nt && j < nt && (with_q ? i <= j : i < j)) {
+          const float* ki = base + (DELTA_TT + i) * DKP;
+          const float* xj = base + (with_q ? j : DELTA_TT + j) * DKP;
+          for (int d = lane; d < dk; d += 32) acc = fmaf(ki[d], xj[d], acc);
+          acc = warp_sum(acc);
+        }
+        if (lane == 0) dots[e] = acc;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        float beta[B], g[B];
+        for (int j = 0; j < B; ++j) {
+          beta[j] = j < nt ? a.prep[(size_t)(t0 + j) * P + Cc + h] : 0.f;
+          g[j] = j < nt ? a.prep[(size_t)(t0 + j) * P + Cc + H + h] : 1.f;
+        }
+        delta_group_scalars(sm + st * STAGE + 2 * DELTA_TT * DKP + DELTA_TT * DELTA_COLS, dots, beta, g);
+      }
+      __syncthreads();
+    }
     for (int g0 = 0; g0 < nt; g0 += B) {
       float k[B][R], sk[B], sq[B];
 #pragma unroll
@@ -380,9 +434,15 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
   pdl_launch_dependents_if_large();
   if (sp) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int e = ((i >> 2) * DELTA_LANES + l) * 4 + (i & 3);
-      if (e < dk) sp[e] = S[i];
+    for (int i = 0; i < R / 4; ++i) {
+      const int e = (i * DELTA_LANES + l) * 4;
+      if (wide_state) {
+        if (e < dk) *reinterpret_cast<float4*>(sp + e) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+          if (e + x < dk) sp[e + x] = S[4 * i + x];
+      }
     }
   }
 }
@@ -404,6 +464,12 @@ __global__ void delta_finish_kernel(const DeltaArgs a) {
     const float inv = 1.0f / sqrtf(ss / (float)dv + a.norm_eps);
     T* y = (T*)a.y + ((size_t)t * H + h) * dv;
     for (int j = lane; j < dv; j += 32) y[j] = from_f32<T>(o[j] * inv * a.norm_w[j] * silu_f(gate[j]));
+  }
+  // the block of a sequence's first row also keeps the convolutions' tail (every reader
+  // of the old one, the prepare kernel, has finished)
+  if (a.taps > 1) {
+    const int seq = a.token_seq[t];
+    if (t == a.cu_q[seq]) delta_keep_tail(a, seq);
   }
   pdl_launch_dependents_if_large();
 }
@@ -438,17 +504,14 @@ static int delta_forward(const DeltaArgs& a, cudaStream_t s) {
   int e = delta_check(a);
   if (e) return e;
   if (a.n_tokens == 0) return 0;
-  const int Cc = 2 * a.G * a.dk + a.H * a.dv;
   const int units = a.G + (a.H * a.dv + DELTA_PREP_V - 1) / DELTA_PREP_V;
   e = gb_launch(delta_prepare_kernel, dim3(a.n_tokens, units), dim3(256),
                 (size_t)2 * a.dk * sizeof(float), s, a);
   if (e) return e;
-  if (a.taps > 1) {
-    e = gb_launch(delta_keep_kernel, dim3(a.n_seqs, (Cc + 1023) / 1024), dim3(256), 0, s, a);
+  if (!a.few_rows) {
+    e = gb_launch(delta_gram_kernel, dim3(a.n_tokens, a.H), dim3(128), 0, s, a);
     if (e) return e;
   }
-  e = gb_launch(delta_gram_kernel, dim3(a.n_tokens, a.H), dim3(128), 0, s, a);
-  if (e) return e;
   const int per_lane = (a.dk + DELTA_LANES - 1) / DELTA_LANES;
   if (per_lane <= 4) e = scan_launch<4>(a, s);
   else if (per_lane <= 8) e = scan_launch<8>(a, s);
@@ -456,10 +519,13 @@ static int delta_forward(const DeltaArgs& a, cudaStream_t s) {
   else e = scan_launch<16>(a, s);
   if (e) return e;
   const int warps = a.H < 8 ? a.H : 8;
-  return gb_launch(delta_finish_kernel<T>, dim3(a.n_tokens, (a.H + warps - 1) / warps),
-                   dim3(warps * 32), 0, s, a);
+  int rows_y = (a.H + warps - 1) / warps;            // blocks of a row: enough for its heads, and
+  const int Cc = 2 * a.G * a.dk + a.H * a.dv;        //   for the tail's channels four to a thread
+  const int for_tail = a.taps > 1 ? (Cc + warps * 32 * 4 - 1) / (warps * 32 * 4) : 1;
+  if (for_tail > rows_y) rows_y = for_tail < 64 ? for_tail : 64;
+  return gb_launch(delta_finish_kernel<T>, dim3(a.n_tokens, rows_y), dim3(warps * 32), 0, s, a);
 }
 
-// Five launches: prepare, keep (with more than one tap), gram, scan, finish.
+// Four launches: prepare, gram (not for a step of few rows a sequence), scan, finish.
 GB_EXPORT int gb_delta_forward_f32(const DeltaArgs* a, cudaStream_t s) { return delta_forward<float>(*a, s); }
 GB_EXPORT int gb_delta_forward_bf16(const DeltaArgs* a, cudaStream_t s) { return delta_forward<bf16>(*a, s); }

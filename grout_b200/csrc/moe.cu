@@ -42,9 +42,14 @@ struct MoeArgs {
 
 #define MOE_MAX_OUTPUTS 1024
 
+#define MOE_ROUTE_THREADS 256
+#define MOE_ROUTE_CHUNK 8     // router outputs whose sums a thread carries side by side
+
 template <typename T>
-__global__ void moe_route_kernel(const MoeArgs a) {
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeArgs a) {
   extern __shared__ float sm[];   // z [n_all], c [n_all]
+  __shared__ float part[MOE_ROUTE_THREADS / 32][MOE_ROUTE_CHUNK];
+  __shared__ float gbest[MOE_MAX_OUTPUTS];
   pdl_launch_dependents_if_small();
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -53,14 +58,34 @@ __global__ void moe_route_kernel(const MoeArgs a) {
   float* z = sm;
   float* c = sm + n_all;
   const T* x = (const T*)a.x + (size_t)t * W;
-  for (int e = warp; e < n_all; e += nwarps) {
-    const float* w = a.router_w + (size_t)e * W;
-    float acc = 0.f;
-    for (int i = lane; i < W; i += 32) acc = fmaf(to_f32<T>(x[i]), w[i], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+  // every thread takes a slice of the row against a few router rows at a time, so that
+  // all of a slice's loads are under way together; the sums are put together in a fixed
+  // order (lanes by the shuffle tree, then warp after warp)
+  for (int e0 = 0; e0 < n_all; e0 += MOE_ROUTE_CHUNK) {
+    float acc[MOE_ROUTE_CHUNK];
+#pragma unroll
+    for (int u = 0; u < MOE_ROUTE_CHUNK; ++u) acc[u] = 0.f;
+    const int nu = min(MOE_ROUTE_CHUNK, n_all - e0);
+#pragma unroll 4
+    for (int i = tid; i < W; i += MOE_ROUTE_THREADS) {
+      const float xv = to_f32<T>(x[i]);
+#pragma unroll
+      for (int u = 0; u < MOE_ROUTE_CHUNK; ++u)
+        if (u < nu) acc[u] = fmaf(xv, a.router_w[(size_t)(e0 + u) * W + i], acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < MOE_ROUTE_CHUNK; ++u) {
+      const float v = warp_sum(acc[u]);
+      if (lane == 0) part[warp][u] = v;
+    }
+    __syncthreads();
+    if (tid < MOE_ROUTE_CHUNK && e0 + tid < n_all) {
+      float v = 0.f;
+      for (int w = 0; w < nwarps; ++w) v += part[w][tid];
+      z[e0 + tid] = v;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   if (tid == 0) {
     float mx = -INFINITY, sum = 0.f;
     for (int e = 0; e < n_all; ++e) mx = fmaxf(mx, z[e]);
@@ -70,21 +95,20 @@ __global__ void moe_route_kernel(const MoeArgs a) {
       const int per = n_all / a.n_groups;
       // drop the groups that are not among the best: n_groups - keep_groups times the worst
       // remaining one (of equal groups the later one goes first)
-      unsigned long long dropped[MOE_MAX_OUTPUTS / 64] = {0};
+      float* best = gbest;                       // a group's best choice score; NaN once dropped
+      for (int g = 0; g < a.n_groups; ++g) {
+        float b = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+        best[g] = b;
+      }
       for (int d = 0; d < a.n_groups - a.keep_groups; ++d) {
         int worst = -1;
         float worst_v = INFINITY;
-        for (int g = 0; g < a.n_groups; ++g) {
-          if (dropped[g >> 6] >> (g & 63) & 1ull) continue;
-          float best = -INFINITY;
-          for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
-          if (best <= worst_v) { worst_v = best; worst = g; }
-        }
-        dropped[worst >> 6] |= 1ull << (worst & 63);
+        for (int g = 0; g < a.n_groups; ++g)
+          if (!isnan(best[g]) && best[g] <= worst_v) { worst_v = best[g]; worst = g; }
+        best[worst] = NAN;
+        for (int e = worst * per; e < (worst + 1) * per; ++e) c[e] = -INFINITY;
       }
-      for (int g = 0; g < a.n_groups; ++g)
-        if (dropped[g >> 6] >> (g & 63) & 1ull)
-          for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
     }
     for (int j = 0; j < a.top; ++j) {   // the largest first; of equal ones the earlier
       int best = 0;
@@ -95,10 +119,13 @@ __global__ void moe_route_kernel(const MoeArgs a) {
       c[best] = NAN;                    // taken
       a.ids[(size_t)t * a.top + j] = best;
       a.wts[(size_t)t * a.top + j] = z[best];
-      a.rank[(size_t)t * a.top + j] = best < a.E ? atomicAdd(&a.counts[best], 1) : -1;
     }
   }
   __syncthreads();
+  for (int j = tid; j < a.top; j += blockDim.x) {   // the choices' places among their experts' pairs
+    const int e = a.ids[(size_t)t * a.top + j];
+    a.rank[(size_t)t * a.top + j] = e < a.E ? atomicAdd(&a.counts[e], 1) : -1;
+  }
   pdl_launch_dependents_if_large();
   for (int j = 0; j < a.top; ++j) {     // experts that hand their input on
     if (a.ids[(size_t)t * a.top + j] < a.E) continue;
@@ -257,7 +284,8 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
 // A block of four warps takes a tile of BM pairs and 64 output columns (mma.sync m16n8k16,
 // 32-bit sums).  With BM = 64 (many tokens) a warp owns 16 of the rows and all 64 columns;
 // with BM = 16 (a decode step: a handful of pairs per expert, the weights' bytes are the
-// cost) the warps share the 16 rows and take 16 columns each.  Rows of the activations
+// cost) the tile is 32 columns wide, so that more blocks stream weights at once, and the
+// warps share the 16 rows and take 8 columns each.  Rows of the activations
 // (gathered by token for the first product, in list order for the second) and rows of the
 // expert's weight reach shared memory by 16-byte asynchronous copies, STAGES chunks of 64
 // columns of the inner size in flight; rows and columns beyond the tile's end are filled
@@ -267,19 +295,25 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
 #define MT_BK 64
 #define MT_LD (MT_BK + 8)
 
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+
 template <bool UP, int BM>
 struct MoeTile {
   static constexpr int NB = UP ? 2 : 1;
+  static constexpr int BN = BM == 64 ? MT_BN : 32;
   static constexpr int STAGES = BM == 64 ? 3 : 4;
-  static constexpr int STAGE_ELEMS = (BM + NB * MT_BN) * MT_LD;
+  static constexpr int STAGE_ELEMS = (BM + NB * BN) * MT_LD;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_ELEMS * sizeof(bf16);
 };
 
 template <bool UP, int BM>
 __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   using Tile = MoeTile<UP, BM>;
-  constexpr int NB = Tile::NB, STAGES = Tile::STAGES;
-  constexpr int NJ = BM == 64 ? 8 : 2;          // 8-column pieces of a warp's share
+  constexpr int NB = Tile::NB, STAGES = Tile::STAGES, BN = Tile::BN;
+  constexpr int NJ = BM == 64 ? 8 : 1;          // 8-column pieces of a warp's share
   extern __shared__ __align__(16) bf16 tiles[];
   __shared__ int src_row[BM];
   pdl_launch_dependents_if_small();
@@ -288,7 +322,7 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   if (!moe_find_tile<BM>(a.offsets, a.E, blockIdx.x, e, first, n_rows)) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = UP ? a.W : a.F, N = UP ? a.F : a.W;
-  const int n0 = blockIdx.y * MT_BN;
+  const int n0 = blockIdx.y * BN;
   if (tid < BM) {
     int r = -1;
     if (tid < n_rows) r = UP ? a.perm[first + tid] / a.top : first + tid;
@@ -307,11 +341,11 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
       cp_async16(As + r * MT_LD + pc, ok ? A + (size_t)src_row[r] * K + kc : A, ok);
     }
 #pragma unroll
-    for (int i = 0; i < MT_BN * 8 / 128; ++i) {
+    for (int i = 0; i < BN * 8 / 128; ++i) {
       const int c = tid + i * 128, r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
       const bool ok = n0 + r < N && kc < K;
       cp_async16(Bs + r * MT_LD + pc, ok ? B0 + (size_t)(n0 + r) * K + kc : B0, ok);
-      if (UP) cp_async16(Bs + (MT_BN + r) * MT_LD + pc, ok ? B1 + (size_t)(n0 + r) * K + kc : B1, ok);
+      if (UP) cp_async16(Bs + (BN + r) * MT_LD + pc, ok ? B1 + (size_t)(n0 + r) * K + kc : B1, ok);
     }
   };
   float acc[NB][NJ][4];
@@ -321,9 +355,10 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
     for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int x = 0; x < 4; ++x) acc[b][j][x] = 0.f;
-  const int row_w = BM == 64 ? warp * 16 : 0, col_w = BM == 64 ? 0 : warp * 16;
+  const int row_w = BM == 64 ? warp * 16 : 0, col_w = BM == 64 ? 0 : warp * 8;
   const int arow = row_w + (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
-  const int brow = col_w + (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
+  // two 8-column pieces at a time (four 8 x 8 blocks), or one (two blocks: lanes 0-15 give the rows)
+  const int brow = col_w + (lane & 7) + (NJ > 1 ? (lane >> 4) * 8 : 0), bcol = ((lane >> 3) & 1) * 8;
   const int nk = (K + MT_BK - 1) / MT_BK;
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {      // a group per stage, empty beyond the end
@@ -342,14 +377,21 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
       uint32_t af[4];
       ldmatrix_x4(af, As + arow * MT_LD + k * 16 + acol);
 #pragma unroll
-      for (int b = 0; b < NB; ++b)
+      for (int b = 0; b < NB; ++b) {
+        if (NJ == 1) {
+          uint32_t bf[2];
+          ldmatrix_x2(bf, Bs + (b * BN + brow) * MT_LD + k * 16 + bcol);
+          mma_16816(acc[b][0], af, bf[0], bf[1]);
+        } else {
 #pragma unroll
-        for (int j = 0; j < NJ; j += 2) {
-          uint32_t bf[4];
-          ldmatrix_x4(bf, Bs + (b * MT_BN + j * 8 + brow) * MT_LD + k * 16 + bcol);
-          mma_16816(acc[b][j], af, bf[0], bf[1]);
-          mma_16816(acc[b][j + 1], af, bf[2], bf[3]);
+          for (int j = 0; j + 1 < NJ; j += 2) {
+            uint32_t bf[4];
+            ldmatrix_x4(bf, Bs + (b * BN + j * 8 + brow) * MT_LD + k * 16 + bcol);
+            mma_16816(acc[b][j], af, bf[0], bf[1]);
+            mma_16816(acc[b][j + 1], af, bf[2], bf[3]);
+          }
         }
+      }
     }
   }
   cp_async_wait<0>();
@@ -395,8 +437,8 @@ static int moe_tc_launch(const MoeArgs& a, long long pairs, cudaStream_t s) {
   const size_t smem = MoeTile<UP, BM>::SMEM;
   cudaError_t ce = cudaFuncSetAttribute(moe_tc_kernel<UP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
-  const int N = UP ? a.F : a.W;
-  return gb_launch(moe_tc_kernel<UP, BM>, dim3((unsigned)tiles, (N + MT_BN - 1) / MT_BN), dim3(128), smem, s, a);
+  const int N = UP ? a.F : a.W, BN = MoeTile<UP, BM>::BN;
+  return gb_launch(moe_tc_kernel<UP, BM>, dim3((unsigned)tiles, (N + BN - 1) / BN), dim3(128), smem, s, a);
 }
 
 static int moe_check(const MoeArgs& a) {
@@ -418,7 +460,7 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
   if (e) return e;
   if (a.T == 0) return 0;
   const int n_all = a.E + a.n_identity;
-  e = gb_launch(moe_route_kernel<T>, dim3(a.T), dim3(128), (size_t)2 * n_all * sizeof(float), s, a);
+  e = gb_launch(moe_route_kernel<T>, dim3(a.T), dim3(MOE_ROUTE_THREADS), (size_t)2 * n_all * sizeof(float), s, a);
   if (e) return e;
   e = gb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, a);
   if (e) return e;

@@ -357,7 +357,25 @@ __global__ void add_postnorm_kernel(const PostNormArgs a) {
   if (has_d) {
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
       float d = din ? to_f32<T>(din[i]) : 0.f;
-      for (int k = 0; k < a.n_parts; ++k) d += pin[(size_t)k * a.part_stride + i];
+      // partial sums are asked for eight (or four) at a time and added in their order: one
+      // trip to memory for the lot instead of one each
+      int k = 0;
+      for (; k + 8 <= a.n_parts; k += 8) {
+        float p[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) p[u] = pin[(size_t)(k + u) * a.part_stride + i];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) d += p[u];
+      }
+      if (k + 4 <= a.n_parts) {
+        float p[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) p[u] = pin[(size_t)(k + u) * a.part_stride + i];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) d += p[u];
+        k += 4;
+      }
+      for (; k < a.n_parts; ++k) d += pin[(size_t)k * a.part_stride + i];
       row[i] = d;
       ss += d * d;
     }

@@ -1347,7 +1347,7 @@ class _DeltaArgs(ctypes.Structure):
                 ("token_seq", _P), ("cu_q", _P), ("slots", _P), ("state", _P), ("state_stride", _L),
                 ("prep", _P), ("o", _P), ("y", _P), ("n_tokens", _I), ("n_seqs", _I), ("H", _I),
                 ("G", _I), ("dk", _I), ("dv", _I), ("taps", _I), ("unit_eps", _F), ("norm_eps", _F),
-                ("prep_stride", _I)]
+                ("prep_stride", _I), ("few_rows", _I)]
 
 
 def delta_state_floats(H: int, G: int, dk: int, dv: int, taps: int) -> int:
@@ -1366,13 +1366,14 @@ def _cost_delta(out, proj, state, *a, H, G, dk, dv, taps, **k):
 def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
                   a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, *, H: int,
                   G: int, dk: int, dv: int, taps: int, unit_eps: float, norm_eps: float,
-                  token_seq, cu_q, slots, dtype: torch.dtype) -> torch.Tensor:
+                  token_seq, cu_q, slots, dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
     """The gated delta rule on the rows of a step.  ``proj`` [T, C] 32-bit: the columns
     q [G dk] | k [G dk] | v [H dv] | gate [H dv] | b [H] | a [H] of the mixer's one
     projection; ``state`` [slots, delta_state_floats] 32-bit, updated in place for the
     sequences whose slot is not negative; ``conv_w`` [2 G dk + H dv, taps].  Returns
     y [T, H dv] in ``dtype``: every head's read-out, normalised over dv, times ``norm_w``
-    and silu(gate)."""
+    and silu(gate).  ``max_rows``: the most rows any sequence of the step brings, when the
+    host knows it (a decode step: 1); steps of at most four rows a sequence take one launch less."""
     _need(proj, "projection", torch.float32, 2)
     _need(state, "state", torch.float32, 2)
     Cc = 2 * G * dk + H * dv
@@ -1406,8 +1407,9 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     a.prep, a.o, a.y = prep.data_ptr(), o.data_ptr(), y.data_ptr()
     a.n_tokens, a.n_seqs, a.H, a.G, a.dk, a.dv, a.taps = T, n_seqs, H, G, dk, dv, taps
     a.unit_eps, a.norm_eps, a.prep_stride = float(unit_eps), float(norm_eps), prep_stride
+    a.few_rows = int(max_rows is not None and 0 < max_rows <= 4)
     _check(_fn("delta", f"gb_delta_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "delta_forward", 5 if taps > 1 else 4)
+           "delta_forward", 3 if a.few_rows else 4)
     return y
 
 

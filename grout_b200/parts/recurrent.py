@@ -98,5 +98,5 @@ class GatedDelta(Mixer):
                               self.norm_w, H=self.H, G=self.G, dk=self.dk, dv=self.dv,
                               taps=self.taps, unit_eps=self.unit_eps, norm_eps=self.norm_eps,
                               token_seq=step.token_seq, cu_q=step.cu_q, slots=step.slots,
-                              dtype=self.ctx.dtype)
+                              dtype=self.ctx.dtype, max_rows=step.max_q_len)
         return self.o(y, partial_ok=True)
