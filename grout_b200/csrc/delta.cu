@@ -22,8 +22,8 @@
 //            with them and the group's g and beta every scalar of the group that
 //            does not depend on the column
 //   scan     the recurrence.  The columns of S are independent recurrences, so a
-//            column is held in the registers of 16 lanes (dk / 16 elements each),
-//            8 columns a block, and a sequence's rows are walked in order, four
+//            column is held in the registers of 8 lanes (dk / 8 elements each),
+//            16 columns a block, and a sequence's rows are walked in order, four
 //            at a time: with c_j = g_1 .. g_j and s_0 the column before the group,
 //              s_{j-1} . k_j = c_{j-1} (s_0 . k_j) + sum_{i<j} (c_{j-1} / c_i) (k_i . k_j) u_i
 //              o_j = c_j (s_0 . q_j) + sum_{i<=j} (c_j / c_i) (k_i . q_j) u_i
@@ -170,8 +170,8 @@ __device__ __forceinline__ void delta_keep_tail(const DeltaArgs& a, int seq) {
   }
 }
 
-#define DELTA_LANES 16      // lanes that share a column of S
-#define DELTA_COLS 8        // columns of S per block
+#define DELTA_LANES 8       // lanes that share a column of S
+#define DELTA_COLS 16       // columns of S per block
 #define DELTA_TT 16         // tokens whose operands are staged together
 #define DELTA_B 4           // rows of a group
 
@@ -251,7 +251,7 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 }
 
 // R floats of a column per lane, in pieces of four: piece i of lane l holds the
-// elements (i * 16 + l) * 4 .. + 3, so that the lanes of a column read contiguous
+// elements (i * 8 + l) * 4 .. + 3, so that the lanes of a column read contiguous
 // bytes of shared memory, and of the state, at a time.
 template <int R>
 __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(const DeltaArgs a) {
@@ -270,8 +270,8 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
   const int gram_off = delta_gram_offset(Cc, H);
   const int kvh = h / (H / G);
   const bool active = col < dv;
-  if (dk < DKP)
-    for (int i = tid; i < 2 * STAGE; i += blockDim.x) sm[i] = 0.f;   // what no copy writes stays zero
+  if (dk < DKP)   // what no copy writes stays zero (a step of few rows has one stage only)
+    for (int i = tid; i < (a.few_rows ? 1 : 2) * STAGE; i += blockDim.x) sm[i] = 0.f;
   pdl_wait();
   const int row0 = a.cu_q[seq], n = a.cu_q[seq + 1] - row0;
   if (n <= 0) return;
@@ -333,6 +333,15 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     }
   };
   const int n_chunks = (n + DELTA_TT - 1) / DELTA_TT;
+  float beta_f[B], g_f[B];      // a step of few rows: the one group's beta and g, asked for early
+#pragma unroll
+  for (int j = 0; j < B; ++j) {
+    beta_f[j] = 0.f, g_f[j] = 1.f;
+    if (a.few_rows && tid == 0 && j < n) {
+      beta_f[j] = a.prep[(size_t)(row0 + j) * P + Cc + h];
+      g_f[j] = a.prep[(size_t)(row0 + j) * P + Cc + H + h];
+    }
+  }
   stage_in(0, 0);
   for (int c = 0; c < n_chunks; ++c) {
     const int st = c & 1;
@@ -362,14 +371,8 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
         if (lane == 0) dots[e] = acc;
       }
       __syncthreads();
-      if (tid == 0) {
-        float beta[B], g[B];
-        for (int j = 0; j < B; ++j) {
-          beta[j] = j < nt ? a.prep[(size_t)(t0 + j) * P + Cc + h] : 0.f;
-          g[j] = j < nt ? a.prep[(size_t)(t0 + j) * P + Cc + H + h] : 1.f;
-        }
-        delta_group_scalars(sm + st * STAGE + 2 * DELTA_TT * DKP + DELTA_TT * DELTA_COLS, dots, beta, g);
-      }
+      if (tid == 0)
+        delta_group_scalars(sm + st * STAGE + 2 * DELTA_TT * DKP + DELTA_TT * DELTA_COLS, dots, beta_f, g_f);
       __syncthreads();
     }
     for (int g0 = 0; g0 < nt; g0 += B) {
@@ -477,8 +480,8 @@ __global__ void delta_finish_kernel(const DeltaArgs a) {
 template <int R>
 static int scan_launch(const DeltaArgs& a, cudaStream_t s) {
   const dim3 grid((a.dv + DELTA_COLS - 1) / DELTA_COLS, a.H, a.n_seqs), block(DELTA_LANES * DELTA_COLS);
-  const size_t smem = (size_t)2 * (DELTA_TT * (2 * DELTA_LANES * R + DELTA_COLS) +
-                                   (DELTA_TT / DELTA_B) * DELTA_COEF) * sizeof(float);
+  const size_t smem = (size_t)(a.few_rows ? 1 : 2) * (DELTA_TT * (2 * DELTA_LANES * R + DELTA_COLS) +
+                                                      (DELTA_TT / DELTA_B) * DELTA_COEF) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t ce = cudaFuncSetAttribute(delta_scan_kernel<R>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -491,7 +494,7 @@ static int delta_check(const DeltaArgs& a) {
   if (a.n_tokens < 0 || a.n_seqs <= 0 || a.H <= 0 || a.G <= 0 || a.H % a.G || a.dk <= 0 ||
       a.dv <= 0 || a.taps <= 0 || !a.proj || !a.state || !a.prep || !a.o || !a.y)
     return GB_ERR_BAD_ARG;
-  if (a.dk > 16 * DELTA_LANES) return GB_ERR_UNSUPPORTED;
+  if (a.dk > 32 * DELTA_LANES) return GB_ERR_UNSUPPORTED;
   const int Cc = 2 * a.G * a.dk + a.H * a.dv;
   if (a.prep_stride != delta_gram_offset(Cc, a.H) + DELTA_COEF * a.H ||
       (((uintptr_t)a.prep) & 15))
@@ -516,7 +519,9 @@ static int delta_forward(const DeltaArgs& a, cudaStream_t s) {
   if (per_lane <= 4) e = scan_launch<4>(a, s);
   else if (per_lane <= 8) e = scan_launch<8>(a, s);
   else if (per_lane <= 12) e = scan_launch<12>(a, s);
-  else e = scan_launch<16>(a, s);
+  else if (per_lane <= 16) e = scan_launch<16>(a, s);
+  else if (per_lane <= 24) e = scan_launch<24>(a, s);
+  else e = scan_launch<32>(a, s);
   if (e) return e;
   const int warps = a.H < 8 ? a.H : 8;
   int rows_y = (a.H + warps - 1) / warps;            // blocks of a row: enough for its heads, and

@@ -91,7 +91,8 @@ struct TcArgs {
   int* error;           // device int, 0 while all is well
   int rowsA, rowsB, K, ld;
   int transpose_out, out_f32;
-  int silu;             // 1 (transposed output only): rows of A are gate|up interleaved in eights;
+  int silu;             // 1 (transposed output only): rows of A are gate|up interleaved in eights,
+                        // the output is silu(gate) * up; 3: the same with the tanh form of gelu;
                         // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
   unsigned long long* stamps;   // optional [blocks][8] %globaltimer stamps of the phases, or null
@@ -185,6 +186,16 @@ struct TcConfig {
   static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TC_BM >> 4) << 24);
 };
+
+// The gate's activation of a gate|up epilogue: silu, g / (1 + e^-g), or (kind 3) the tanh
+// form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))), tanh(x) = 1 - 2 / (e^2x + 1).
+__device__ __forceinline__ float tc_gate_act(float g, int kind) {
+  if (kind == 3) {
+    const float e = __expf(1.5957691216057308f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (2.0f - __fdividef(2.0f, e + 1.0f));
+  }
+  return __fdividef(g, 1.0f + __expf(-g));
+}
 
 template <int BN, int LEAN = 0>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -469,7 +480,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // put together in shared memory instead and written as whole 128-byte rows.  (At the
       // 4B sizes and batch 64 the epilogue of the one tile a block has is not hidden behind
       // anything: 3.6 of the product's 22 us.)
-      const bool staged = Cfg::EPI_BYTES > 0 && a.transpose_out && a.silu == 1 && !a.out_f32 && (a.ld & 7) == 0 &&
+      const bool staged = Cfg::EPI_BYTES > 0 && a.transpose_out && (a.silu & 1) && !a.out_f32 && (a.ld & 7) == 0 &&
                           (((uintptr_t)a.out) & 15) == 0;
       if (write_out) {
 #pragma unroll 1
@@ -520,7 +531,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
           // store 16 columns of row r
-          if (a.transpose_out && a.silu == 1) {
+          if (a.transpose_out && (a.silu & 1)) {
             // rows 16t..16t+7 of A are gates and 16t+8..16t+15 the matching ups: the up
             // of this lane's gate sits 8 lanes further; out[col_b][feature] = silu(g) * u
             // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296, as an epilogue)
@@ -542,7 +553,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
-                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                const float val = tc_gate_act(f[j], a.silu) * up;
                 st_f32_if(pf, val, mine && j < valid);
                 pf += ld;
               }
@@ -554,7 +565,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
-                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                const float val = tc_gate_act(f[j], a.silu) * up;
                 asm volatile("{ .reg .pred q; setp.ne.b32 q, %2, 0; @q st.shared.b16 [%0], %1; }" ::"r"(sp + j * 128),
                              "h"(__bfloat16_as_ushort(__float2bfloat16_rn(val))), "r"((int)gate_lane)
                              : "memory");
@@ -564,7 +575,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int j = 0; j < 16; ++j) {
                 const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
                 // bf16 output: the fast exponential and division are far inside its rounding
-                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                const float val = tc_gate_act(f[j], a.silu) * up;
                 st_bf16_if(pb, __float2bfloat16_rn(val), mine && j < valid);
                 pb += ld;
               }
@@ -881,8 +892,8 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   if (e) return e;
   if (!A || !B || !args->out || !args->scratch || !args->counters || !args->error) return GB_ERR_BAD_ARG;
   if ((((uintptr_t)A) | ((uintptr_t)B)) & 15) return GB_ERR_BAD_ARG;
-  if (args->silu == 1 && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
-  if (args->silu < 0 || args->silu > 2) return GB_ERR_BAD_ARG;
+  if ((args->silu & 1) && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
+  if (args->silu < 0 || args->silu > 3) return GB_ERR_BAD_ARG;
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;

@@ -47,7 +47,7 @@ struct Tc2Args {
   int* error;    // device int, 0 while all is well
   int M, N, K, ld;
   int out_f32;
-  int silu;      // 1: columns of W^T are gate|up interleaved in eights; out is [M, N / 2]
+  int silu;      // 1: columns of W^T are gate|up interleaved in eights; out is [M, N / 2]; 3: the same with gelu (tanh form)
                  // 2: every output becomes max(x, 0)^2 (a feed-forward without a gate)
   int bn;        // columns of C per tile: a multiple of 16, 32..256 (filled in by the launcher)
 };
@@ -104,7 +104,14 @@ __device__ __forceinline__ void tc_commit_pair(void* bar) {
       : "memory");
 }
 
-__device__ __forceinline__ float t2_silu(float g) { return g / (1.0f + __expf(-g)); }
+// silu, or (kind 3) the tanh form of gelu with tanh(x) = 1 - 2 / (e^2x + 1)
+__device__ __forceinline__ float t2_gate(float g, int kind) {
+  if (kind == 3) {
+    const float e = __expf(1.5957691216057308f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (2.0f - __fdividef(2.0f, e + 1.0f));
+  }
+  return g / (1.0f + __expf(-g));
+}
 
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -227,7 +234,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // ------------------------------------------------------------------ epilogue (both blocks)
     const int q = warp & 3;   // the TMEM lanes this warp may touch
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int n_out = a.silu == 1 ? a.N / 2 : a.N;
+    const int n_out = (a.silu & 1) ? a.N / 2 : a.N;
     int t = 0;
     bool ok = true;
     for (int tile = cluster; tile < n_tiles && ok; tile += n_clusters, ++t) {
@@ -257,13 +264,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             v[c] = __float_as_uint(p * p);
           }
         }
-        if (a.silu == 1) {
+        if (a.silu & 1) {
           uint32_t w[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float g0 = __uint_as_float(v[2 * i]), g1 = __uint_as_float(v[2 * i + 1]);
             const float u0 = __uint_as_float(v[8 + 2 * i]), u1 = __uint_as_float(v[8 + 2 * i + 1]);
-            w[i] = pack2(t2_silu(g0) * u0, t2_silu(g1) * u1);
+            w[i] = pack2(t2_gate(g0, a.silu) * u0, t2_gate(g1, a.silu) * u1);
           }
           *reinterpret_cast<uint4*>((bf16*)a.out + (size_t)row * a.ld + col / 2) = make_uint4(w[0], w[1], w[2], w[3]);
         } else if (a.out_f32) {
@@ -329,8 +336,8 @@ GB_EXPORT int gb_gemm_tc2_bf16(const void* X, const void* W, const Tc2Args* args
   if (!X || !W || !a.out || !a.error || a.M <= 0 || a.N <= 0 || a.K <= 0) return GB_ERR_BAD_ARG;
   if (a.K % 8) return GB_ERR_UNSUPPORTED;
   if ((((uintptr_t)X) | ((uintptr_t)W) | ((uintptr_t)a.out)) & 15) return GB_ERR_BAD_ARG;
-  if (a.silu == 1 && (a.N % 16 || a.out_f32)) return GB_ERR_UNSUPPORTED;
-  if (a.silu < 0 || a.silu > 2) return GB_ERR_BAD_ARG;
+  if ((a.silu & 1) && (a.N % 16 || a.out_f32)) return GB_ERR_UNSUPPORTED;
+  if (a.silu < 0 || a.silu > 3) return GB_ERR_BAD_ARG;
   if ((a.ld * (a.out_f32 ? 4 : 2)) % 16) return GB_ERR_UNSUPPORTED;
   static int sms = 0;
   static bool configured = false;
