@@ -831,7 +831,7 @@ def tc_wait_selftest(device, limit_us: int = 1000) -> int:
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                  swap: Optional[bool] = None, silu_mul: bool = False,
                  stamps: Optional[torch.Tensor] = None, split_out: bool = False,
-                 relu_squared: bool = False) -> torch.Tensor:
+                 relu_squared: bool = False, gate_act: str = "silu") -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
@@ -842,7 +842,10 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     products are returned as [S, M, N] for the consumer to add (its norm or q/k
     preparation does so in the kernel it runs anyway); otherwise the result is the
     ordinary [M, N].  ``relu_squared``: every output becomes max(y, 0)^2, squared in
-    32-bit before the rounding (not with ``silu_mul`` or ``split_out``)."""
+    32-bit before the rounding (not with ``silu_mul`` or ``split_out``).  ``gate_act``
+    (with ``silu_mul``): "silu" or "gelu_tanh", the activation the gate passes through."""
+    if gate_act not in ("silu", "gelu_tanh"):
+        raise KernelError(f"gate activation '{gate_act}': 'silu' or 'gelu_tanh'")
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -882,12 +885,12 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
         a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32 or bool(split))
         a.split_k = split
-        a.silu = 2 if relu_squared else int(silu_mul)
+        a.silu = 2 if relu_squared else ((3 if gate_act == "gelu_tanh" else 1) if silu_mul else 0)
         a.dep_b = int(swap)                             # the activations are another kernel's output
         a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
             A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16",
-            detail=f" {N}x{K}" + (" silu" if silu_mul else "") + (" relu2" if relu_squared else "") +
+            detail=f" {N}x{K}" + ((" " + gate_act) if silu_mul else "") + (" relu2" if relu_squared else "") +
             (f" split {split}" if split else ""))
     return y
 
@@ -929,12 +932,15 @@ def gemm_tc2_pays(M: int, N: int, device, fused_silu: bool) -> bool:
 @_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                   silu_mul: bool = False, tile_cols: int = 0,
-                  relu_squared: bool = False) -> torch.Tensor:
+                  relu_squared: bool = False, gate_act: str = "silu") -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
     tiles of 256 rows and ``tile_cols`` columns: a multiple of 16 up to 256, by
     default chosen by the kernel's launcher for the shape).  ``silu_mul``: the rows of ``w`` are gate and up rows
     interleaved in groups of 8 and the result is silu(gate) * up, [M, N / 2].
-    ``relu_squared`` (instead): every output becomes max(y, 0)^2, squared in 32-bit."""
+    ``relu_squared`` (instead): every output becomes max(y, 0)^2, squared in 32-bit.
+    ``gate_act`` (with ``silu_mul``): "silu" or "gelu_tanh"."""
+    if gate_act not in ("silu", "gelu_tanh"):
+        raise KernelError(f"gate activation '{gate_act}': 'silu' or 'gelu_tanh'")
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -959,7 +965,7 @@ def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     a.out, a.error = y.data_ptr(), _tc_error_flag(x.device).data_ptr()
     a.M, a.N, a.K, a.ld = M, N, K, n_out
     a.out_f32, a.bn = int(out_dtype == torch.float32), int(tile_cols)
-    a.silu = 2 if relu_squared else int(silu_mul)
+    a.silu = 2 if relu_squared else ((3 if gate_act == "gelu_tanh" else 1) if silu_mul else 0)
     with torch.cuda.device(x.device):
         _check(_fn("gemm_tc2", "gb_gemm_tc2_bf16", "pppp")(
             x.data_ptr(), w.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc2_bf16")

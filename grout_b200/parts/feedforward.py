@@ -111,6 +111,7 @@ class GatedMLP(FeedForward):
         self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight",
                            "down": "down_proj.weight"}, **(names or {}))
         self.gate_up = self.down = None
+        self.interleave = 0
 
     def param_specs(self):
         nm = self.names
@@ -122,7 +123,16 @@ class GatedMLP(FeedForward):
         g, u = params[self.names["gate"]], params[self.names["up"]]
         if g.dtype != u.dtype:
             raise ValueError("gate and up projections must be stored in one dtype to be fused")
-        self.gate_up = Linear(torch.cat([g, u], dim=0), self.ctx.products)
+        # bf16: rows interleaved in groups of 8 (8 gates, their 8 ups, ...), the layout in
+        # which the tcgen05 products apply the activation before they store
+        self.interleave = 8 if (g.dtype == torch.bfloat16 and self.intermediate % 8 == 0
+                                and self.hidden % 8 == 0) else 0
+        if self.interleave:
+            k = self.interleave
+            fused = torch.stack([g.view(-1, k, self.hidden), u.view(-1, k, self.hidden)], dim=1)
+            self.gate_up = Linear(fused.reshape(2 * self.intermediate, self.hidden), self.ctx.products)
+        else:
+            self.gate_up = Linear(torch.cat([g, u], dim=0), self.ctx.products)
         self.down = Linear(params[self.names["down"]], self.ctx.products)
 
     def kernel_modules(self):
@@ -132,9 +142,7 @@ class GatedMLP(FeedForward):
         return True
 
     def forward(self, x, step):
-        gu = self.gate_up(x)
-        h = ops.silu_mul(gu, 0) if self.activation == "silu" else ops.gelu_tanh_mul(gu, 0)
-        return self.down(h, partial_ok=True)
+        return self.down(self.gate_up.silu_mul(x, self.interleave, self.activation), partial_ok=True)
 
 
 @register_part("feedforward", "routed_experts")

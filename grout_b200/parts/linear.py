@@ -84,11 +84,14 @@ class Linear:
                 return ops.gemm_tc2_bf16(x, w, out_dtype)
         return ops.library_mm(x, w, out_dtype)
 
-    def silu_mul(self, x: torch.Tensor, interleave: int) -> torch.Tensor:
-        """silu(gate) * up of a fused gate|up weight.  ``interleave`` 0: gate rows
-        first, then up rows; 8: groups of 8 gate rows followed by their 8 up rows,
-        which lets the decode kernel finish the product in its epilogue."""
+    def silu_mul(self, x: torch.Tensor, interleave: int, activation: str = "silu") -> torch.Tensor:
+        """act(gate) * up of a fused gate|up weight, ``activation`` "silu" or
+        "gelu_tanh".  ``interleave`` 0: gate rows first, then up rows; 8: groups of 8
+        gate rows followed by their 8 up rows, which lets the tcgen05 kernels finish
+        the product in their epilogue."""
         w = self.weight
+        if activation != "silu":
+            return self._gated(x, interleave, activation)
         if (interleave == 8 and w.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS
                 and self.in_features % 8 == 0):
             if self.decode_kernel == "tc":
@@ -101,6 +104,23 @@ class Linear:
                       ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True)))):
             return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)
+
+    def _gated(self, x: torch.Tensor, interleave: int, activation: str) -> torch.Tensor:
+        """The gate|up product with another activation than silu: the tcgen05 kernels
+        have it as an epilogue (the mma.sync decode kernel has not), under the rules of
+        ``silu_mul``; elsewhere the product and an elementwise kernel."""
+        w = self.weight
+        fusable = (interleave == 8 and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+                   and self.in_features % 8 == 0)
+        if fusable and x.shape[0] <= ops.SKINNY_MAX_ROWS and self.decode_kernel == "tc":
+            return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, silu_mul=True, gate_act=activation)
+        if (fusable and x.shape[0] > ops.SKINNY_MAX_ROWS and self.out_features % 32 == 0
+                and (self.prefill_kernel == "pair" or
+                     (self.prefill_kernel == "auto" and
+                      ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True)))):
+            return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True, gate_act=activation)
+        y = self(x)
+        return ops.gelu_tanh_mul(y, interleave) if activation == "gelu_tanh" else ops.silu_mul(y, interleave)
 
     def relu_squared(self, x: torch.Tensor) -> torch.Tensor:
         """max(x W^T, 0)^2.  Where the product's kernel has the epilogue (the tcgen05

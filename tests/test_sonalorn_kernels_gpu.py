@@ -85,6 +85,29 @@ def test_gelu_tanh_gate():
     close(got, plain.gelu_tanh(gu[:, :24].double()) * gu[:, 24:].double(), torch.float32)
 
 
+@pytest.mark.parametrize("rows", [3, 64, 300])
+def test_gelu_tanh_gate_as_the_products_epilogue(rows):
+    """The gated feed-forward part in bfloat16: a decode step's product and a prompt's
+    apply the gate's activation before they store (gate and up rows interleaved in eights);
+    all product choices give the plain result."""
+    from grout_b200.parts import BuildContext, PartSpec, ProductChoice, build_part
+    W, F = 64, 96
+    w = {"gate": rnd(F, W, seed=1, scale=0.3).bfloat16(), "up": rnd(F, W, seed=2, scale=0.3).bfloat16(),
+         "down": rnd(W, F, seed=3, scale=0.2).bfloat16()}
+    x = rnd(rows, W, seed=4).bfloat16()
+    want = plain.dense_ff(x, {"m." + k: v for k, v in w.items()}, "m.")
+    for choice in (ProductChoice("tc", "auto"), ProductChoice("tc", "pair"), ProductChoice("skinny", "library")):
+        part = build_part("feedforward", PartSpec("gated_mlp", dict(
+            hidden=W, intermediate=F, activation="gelu_tanh", names={"gate": "gate", "up": "up", "down": "down"})),
+            BuildContext(torch.bfloat16, torch.device(DEV), choice))
+        part.load({k: v.to(DEV) for k, v in w.items()})
+        assert part.interleave == 8
+        got = part.forward(x.to(DEV), None)
+        got = (got.sum(0) if got.dim() == 3 else got).double().cpu()
+        # the unfused path rounds gate and up before the activation: a bar on the whole
+        assert float((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) < 0.02, (rows, choice)
+
+
 # ------------------------------------------------------------------ the gated delta rule
 def _delta_weights(H, G, dk, dv, taps, W, seed, slow=True):
     g = torch.Generator().manual_seed(seed)
