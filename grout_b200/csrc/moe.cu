@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const MoeArgs a) {
 
 // ---- the two products on the tensor cores (bfloat16, widths that are multiples of 8) ----
 // A block of four warps takes a tile of BM pairs and 64 output columns (mma.sync m16n8k16,
-// 32-bit sums).  With BM = 64 (many tokens) a warp owns 16 of the rows and all 64 columns;
+// 32-bit sums).  With BM = 128 or 64 (many tokens) the warps are two by two, each with half
+// the rows and 32 columns;
 // with BM = 16 (a decode step: a handful of pairs per expert, the weights' bytes are the
 // cost) the tile is 32 columns wide, so that more blocks stream weights at once, and the
 // warps share the 16 rows and take 8 columns each.  Rows of the activations
@@ -303,8 +304,15 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* smem) 
 template <bool UP, int BM>
 struct MoeTile {
   static constexpr int NB = UP ? 2 : 1;
-  static constexpr int BN = BM == 64 ? MT_BN : 32;
-  static constexpr int STAGES = BM == 64 ? 3 : 4;
+  static constexpr int BN = BM >= 64 ? MT_BN : 32;
+  static constexpr int THREADS = 128;
+  // a warp's share of the tile: MI pieces of 16 rows by NJ pieces of 8 columns.  Many rows:
+  // the four warps are two by two, each with half the rows and 32 columns, so that a
+  // fragment read from shared memory feeds several MMAs.  16 rows: the warps share them
+  // and take 8 columns each.
+  static constexpr int MI = BM >= 64 ? BM / 32 : 1;
+  static constexpr int NJ = BM >= 64 ? 4 : 1;
+  static constexpr int STAGES = BM >= 64 ? 3 : 4;
   static constexpr int STAGE_ELEMS = (BM + NB * BN) * MT_LD;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_ELEMS * sizeof(bf16);
 };
@@ -312,8 +320,8 @@ struct MoeTile {
 template <bool UP, int BM>
 __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   using Tile = MoeTile<UP, BM>;
-  constexpr int NB = Tile::NB, STAGES = Tile::STAGES, BN = Tile::BN;
-  constexpr int NJ = BM == 64 ? 8 : 1;          // 8-column pieces of a warp's share
+  constexpr int NB = Tile::NB, STAGES = Tile::STAGES, BN = Tile::BN, NT = Tile::THREADS;
+  constexpr int MI = Tile::MI, NJ = Tile::NJ;
   extern __shared__ __align__(16) bf16 tiles[];
   __shared__ int src_row[BM];
   pdl_launch_dependents_if_small();
@@ -323,10 +331,10 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = UP ? a.W : a.F, N = UP ? a.F : a.W;
   const int n0 = blockIdx.y * BN;
-  if (tid < BM) {
+  for (int i = tid; i < BM; i += NT) {
     int r = -1;
-    if (tid < n_rows) r = UP ? a.perm[first + tid] / a.top : first + tid;
-    src_row[tid] = r;
+    if (i < n_rows) r = UP ? a.perm[first + i] / a.top : first + i;
+    src_row[i] = r;
   }
   __syncthreads();
   const bf16* A = (const bf16*)(UP ? a.x : a.act);
@@ -335,27 +343,30 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   auto load = [&](int stage, int k0) {
     bf16* As = tiles + stage * Tile::STAGE_ELEMS;
     bf16* Bs = As + BM * MT_LD;
-    for (int c = tid; c < BM * 8; c += 128) {            // rows x 8 pieces of 8 elements
+    for (int c = tid; c < BM * 8; c += NT) {             // rows x 8 pieces of 8 elements
       const int r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
       const bool ok = src_row[r] >= 0 && kc < K;
       cp_async16(As + r * MT_LD + pc, ok ? A + (size_t)src_row[r] * K + kc : A, ok);
     }
 #pragma unroll
-    for (int i = 0; i < BN * 8 / 128; ++i) {
-      const int c = tid + i * 128, r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
+    for (int i = 0; i < BN * 8 / NT; ++i) {
+      const int c = tid + i * NT, r = c >> 3, pc = (c & 7) * 8, kc = k0 + pc;
       const bool ok = n0 + r < N && kc < K;
       cp_async16(Bs + r * MT_LD + pc, ok ? B0 + (size_t)(n0 + r) * K + kc : B0, ok);
       if (UP) cp_async16(Bs + (BN + r) * MT_LD + pc, ok ? B1 + (size_t)(n0 + r) * K + kc : B1, ok);
     }
   };
-  float acc[NB][NJ][4];
+  float acc[NB][MI][NJ][4];
 #pragma unroll
   for (int b = 0; b < NB; ++b)
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
+    for (int m = 0; m < MI; ++m)
 #pragma unroll
-      for (int x = 0; x < 4; ++x) acc[b][j][x] = 0.f;
-  const int row_w = BM == 64 ? warp * 16 : 0, col_w = BM == 64 ? 0 : warp * 8;
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[b][m][j][x] = 0.f;
+  const int row_w = BM >= 64 ? (warp >> 1) * (BM / 2) : 0;
+  const int col_w = BM >= 64 ? (warp & 1) * 32 : warp * 8;
   const int arow = row_w + (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
   // two 8-column pieces at a time (four 8 x 8 blocks), or one (two blocks: lanes 0-15 give the rows)
   const int brow = col_w + (lane & 7) + (NJ > 1 ? (lane >> 4) * 8 : 0), bcol = ((lane >> 3) & 1) * 8;
@@ -374,21 +385,26 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
     const bf16* Bs = As + BM * MT_LD;
 #pragma unroll
     for (int k = 0; k < MT_BK / 16; ++k) {
-      uint32_t af[4];
-      ldmatrix_x4(af, As + arow * MT_LD + k * 16 + acol);
+      uint32_t af[MI][4];
+#pragma unroll
+      for (int m = 0; m < MI; ++m) ldmatrix_x4(af[m], As + (arow + m * 16) * MT_LD + k * 16 + acol);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         if (NJ == 1) {
           uint32_t bf[2];
           ldmatrix_x2(bf, Bs + (b * BN + brow) * MT_LD + k * 16 + bcol);
-          mma_16816(acc[b][0], af, bf[0], bf[1]);
+#pragma unroll
+          for (int m = 0; m < MI; ++m) mma_16816(acc[b][m][0], af[m], bf[0], bf[1]);
         } else {
 #pragma unroll
           for (int j = 0; j + 1 < NJ; j += 2) {
             uint32_t bf[4];
             ldmatrix_x4(bf, Bs + (b * BN + j * 8 + brow) * MT_LD + k * 16 + bcol);
-            mma_16816(acc[b][j], af, bf[0], bf[1]);
-            mma_16816(acc[b][j + 1], af, bf[2], bf[3]);
+#pragma unroll
+            for (int m = 0; m < MI; ++m) {
+              mma_16816(acc[b][m][j], af[m], bf[0], bf[1]);
+              mma_16816(acc[b][m][j + 1], af[m], bf[2], bf[3]);
+            }
           }
         }
       }
@@ -398,36 +414,39 @@ __global__ void __launch_bounds__(128) moe_tc_kernel(const MoeArgs a) {
   pdl_launch_dependents_if_large();
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int row = row_w + g + half * 8;
-    if (row >= n_rows) continue;
-    if (UP) {
-      bf16* dst = (bf16*)a.act + (size_t)(first + row) * N;
+  for (int m = 0; m < MI; ++m)
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int col = n0 + col_w + j * 8 + t * 2;
-        float y[2];
+    for (int half = 0; half < 2; ++half) {
+      const int row = row_w + m * 16 + g + half * 8;
+      if (row >= n_rows) continue;
+      if (UP) {
+        bf16* dst = (bf16*)a.act + (size_t)(first + row) * N;
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const float gt = fminf(acc[0][j][half * 2 + x], a.limit);
-          const float up = fminf(fmaxf(acc[NB - 1][j][half * 2 + x], -a.limit), a.limit);
-          y[x] = gt / (1.0f + expf(-a.slope * gt)) * (up + 1.0f);
+        for (int j = 0; j < NJ; ++j) {
+          const int col = n0 + col_w + j * 8 + t * 2;
+          float y[2];
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const float gt = fminf(acc[0][m][j][half * 2 + x], a.limit);
+            const float up = fminf(fmaxf(acc[NB - 1][m][j][half * 2 + x], -a.limit), a.limit);
+            y[x] = gt / (1.0f + expf(-a.slope * gt)) * (up + 1.0f);
+          }
+          if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(y[0], y[1]);
+          else if (col < N) dst[col] = from_f32<bf16>(y[0]);
         }
-        if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(y[0], y[1]);
-        else if (col < N) dst[col] = from_f32<bf16>(y[0]);
-      }
-    } else {
-      const int p = a.perm[first + row], tok = p / a.top, jc = p % a.top;
-      const float w = a.wts[p];
-      float* dst = a.out + ((size_t)jc * a.T + tok) * N;
+      } else {
+        const int p = a.perm[first + row], tok = p / a.top, jc = p % a.top;
+        const float w = a.wts[p];
+        float* dst = a.out + ((size_t)jc * a.T + tok) * N;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int col = n0 + col_w + j * 8 + t * 2;
-        if (col + 1 < N) *reinterpret_cast<float2*>(dst + col) = make_float2(w * acc[0][j][half * 2], w * acc[0][j][half * 2 + 1]);
-        else if (col < N) dst[col] = w * acc[0][j][half * 2];
+        for (int j = 0; j < NJ; ++j) {
+          const int col = n0 + col_w + j * 8 + t * 2;
+          if (col + 1 < N)
+            *reinterpret_cast<float2*>(dst + col) = make_float2(w * acc[0][m][j][half * 2], w * acc[0][m][j][half * 2 + 1]);
+          else if (col < N) dst[col] = w * acc[0][m][j][half * 2];
+        }
       }
     }
-  }
 }
 
 template <bool UP, int BM>
@@ -438,7 +457,8 @@ static int moe_tc_launch(const MoeArgs& a, long long pairs, cudaStream_t s) {
   cudaError_t ce = cudaFuncSetAttribute(moe_tc_kernel<UP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
   const int N = UP ? a.F : a.W, BN = MoeTile<UP, BM>::BN;
-  return gb_launch(moe_tc_kernel<UP, BM>, dim3((unsigned)tiles, (N + BN - 1) / BN), dim3(128), smem, s, a);
+  return gb_launch(moe_tc_kernel<UP, BM>, dim3((unsigned)tiles, (N + BN - 1) / BN),
+                   dim3(MoeTile<UP, BM>::THREADS), smem, s, a);
 }
 
 static int moe_check(const MoeArgs& a) {
@@ -474,6 +494,11 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
       e = moe_tc_launch<true, 16>(a, pairs, s);
       if (e) return e;
       return moe_tc_launch<false, 16>(a, pairs, s);
+    }
+    if (pairs >= 64LL * a.E) {      // 64 pairs an expert and more: tiles of 128 rows
+      e = moe_tc_launch<true, 128>(a, pairs, s);
+      if (e) return e;
+      return moe_tc_launch<false, 128>(a, pairs, s);
     }
     e = moe_tc_launch<true, 64>(a, pairs, s);
     if (e) return e;
