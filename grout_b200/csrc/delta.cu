@@ -29,7 +29,7 @@
 //              o_j = c_j (s_0 . q_j) + sum_{i<=j} (c_j / c_i) (k_i . q_j) u_i
 //              s_4 = c_4 s_0 + sum_i (c_4 / c_i) k_i u_i
 //            so the eight sums over dk that a group needs are taken from the column
-//            as it stands, in one round of shuffles, and what is sequential is a few
+//            as it stands, in one pass of shuffles, and what is sequential is a few
 //            operations on scalars (the quotients are products of the g between, never
 //            divisions).  The operands of 16 tokens at a time (their head's k and q,
 //            the block's 16 values, beta, g, the group's products) reach shared memory

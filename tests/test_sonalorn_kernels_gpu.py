@@ -151,7 +151,8 @@ def _delta_plain(w, m, xs):
 DELTA_SHAPES = [dict(heads=4, kv_heads=2, dim=16, vdim=8, conv=3),
                 dict(heads=3, kv_heads=3, dim=40, vdim=20, conv=4),     # sizes that fill no lane group
                 dict(heads=2, kv_heads=1, dim=64, vdim=48, conv=2),
-                dict(heads=2, kv_heads=2, dim=128, vdim=16, conv=1)]    # no convolution to speak of
+                dict(heads=2, kv_heads=2, dim=128, vdim=16, conv=1),    # no convolution to speak of
+                dict(heads=2, kv_heads=1, dim=30, vdim=10, conv=5)]     # sizes that are no multiple of four
 
 
 @pytest.mark.parametrize("m", DELTA_SHAPES)
