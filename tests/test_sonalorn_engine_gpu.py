@@ -73,6 +73,7 @@ def _layer(kind, mixer, mlp, **kw):
 
 _X1 = _layer("attention", _attn(), _moe(6, 2, 3, 24, 0.6, (4, 2)))
 _Y1 = _layer("delta", _delta(heads=2, kv_heads=2, dim=64, vdim=32, conv=4), _moe(5, 0, 2, 40, 1.5))
+_V1 = _layer("delta", _delta(heads=5, kv_heads=5, dim=30, vdim=18, conv=5), _moe(7, 3, 3, 20, 0.9, (5, 3)))
 SON = {
     # attention first; the last layer runs the first one's tensors; values wider than keys elsewhere
     "S": dict(architecture="Sonalorn", vocab=211, width=64, max_positions=400, norm={"eps": 1e-5},
@@ -93,9 +94,18 @@ SON = {
                       _layer("attention", _attn(heads=6, kv_heads=2, dim=24, vdim=8, scale=0.4,
                                                 q_temp={"coef": 0.3, "every": 1}), {"kind": "dense", "ff": 64}),
                       _layer("attention", _attn(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.1), None)]),
+    # nothing a multiple of eight: the library's product for odd widths, the plain kernels for
+    # experts and for delta heads that fill no 16-byte piece, values wider than keys, five taps,
+    # three of five groups kept, more pass-through outputs, a later layer's tensors used twice
+    "V": dict(architecture="Sonalorn", vocab=173, width=100, max_positions=420, norm={"eps": 2e-5},
+              layers=[_layer("attention", _attn(heads=3, kv_heads=3, dim=40, vdim=56, scale=0.2,
+                                                q_temp={"coef": 0.4, "every": 3}), {"kind": "dense", "ff": 52}),
+                      _V1,
+                      dict(_V1, weights_of=1),
+                      _layer("attention", _attn(heads=6, kv_heads=1, dim=20, vdim=12, scale=0.35, q_temp=None), None)]),
 }
-SEEDS = {"S": 11, "T": 13, "U": 17}
-LENGTHS = {"S": [1, 5, 70, 150], "T": [2, 64, 129, 300], "U": [3, 131, 270]}
+SEEDS = {"S": 11, "T": 13, "U": 17, "V": 19}
+LENGTHS = {"S": [1, 5, 70, 150], "T": [2, 64, 129, 300], "U": [3, 131, 270], "V": [1, 66, 200]}
 
 
 def _sharpen(tensors):
