@@ -11,8 +11,8 @@
 //   out = sum over the chosen of s * y
 //
 // Nothing here needs the host to know how many tokens an expert got, so a step
-// can be captured: `route` chooses and counts, `sort` turns the counts into a
-// list of (token, choice) pairs ordered by expert, and the two products walk
+// can be captured: `route` chooses and counts, and its last block turns the counts into a
+// list of (token, choice) pairs ordered by expert; the two products walk
 // tiles of that list; a block finds its expert from the counts, and blocks
 // beyond the last tile return.  A pair's row is computed the same way wherever it
 // lands in the list, so a token's result does not depend on the batch.  The
@@ -31,7 +31,7 @@ struct MoeArgs {
   int* ids;                 // [T, top] chosen outputs
   float* wts;               // [T, top] their scores
   int* rank;                // [T, top] place of the pair among its expert's pairs
-  int* counts;              // [E] pairs per expert; zero on entry
+  int* counts;              // [E + 1] pairs per expert, and the tickets of `route`'s blocks; zero on entry
   int* offsets;             // [E + 1]
   int* perm;                // [T top] pairs (t * top + j) ordered by expert
   void* act;                // [T top, F] activations of the experts' inner layer, in list order
@@ -133,24 +133,30 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeA
     float* o = a.out + ((size_t)j * a.T + t) * W;
     for (int i = tid; i < W; i += blockDim.x) o[i] = w * to_f32<T>(x[i]);
   }
-}
-
-__global__ void moe_sort_kernel(const MoeArgs a) {
-  pdl_wait();
-  const int tid = threadIdx.x;
+  // The block that finishes last turns the counts into the list of pairs ordered by expert:
+  // every block publishes its choices, then draws a ticket (counts[E]); the one that draws
+  // the last ticket sees all of them.  It leaves the counts and the ticket at zero for the
+  // next call.
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = atomicAdd(&a.counts[a.E], 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   if (tid == 0) {          // few experts: a serial scan is shorter than its set-up
     int run = 0;
-    for (int e = 0; e < a.E; ++e) { a.offsets[e] = run; run += a.counts[e]; }
+    for (int e = 0; e < a.E; ++e) { a.offsets[e] = run; run += __ldcg(&a.counts[e]); }
     a.offsets[a.E] = run;
   }
   __syncthreads();
   const int n_pairs = a.T * a.top;
   for (int p = tid; p < n_pairs; p += blockDim.x) {
-    const int e = a.ids[p];
-    if (e < a.E) a.perm[a.offsets[e] + a.rank[p]] = p;
+    const int e = __ldcg(&a.ids[p]);
+    if (e < a.E) a.perm[a.offsets[e] + __ldcg(&a.rank[p])] = p;
   }
   __syncthreads();
-  for (int e = tid; e < a.E; e += blockDim.x) a.counts[e] = 0;   // zero again for the next call
+  for (int e = tid; e <= a.E; e += blockDim.x) a.counts[e] = 0;
 }
 
 #define MOE_BM 16
@@ -482,8 +488,6 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
   const int n_all = a.E + a.n_identity;
   e = gb_launch(moe_route_kernel<T>, dim3(a.T), dim3(MOE_ROUTE_THREADS), (size_t)2 * n_all * sizeof(float), s, a);
   if (e) return e;
-  e = gb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, a);
-  if (e) return e;
   // the most tiles the pairs can make: every expert may end in a tile that is not full
   const long long pairs = (long long)a.T * a.top;
   if (sizeof(T) == 2 && a.W % 8 == 0 && a.F % 8 == 0 &&
@@ -511,7 +515,7 @@ static int moe_forward(const MoeArgs& a, cudaStream_t s) {
   return gb_launch(moe_down_kernel<T>, dim3((unsigned)tiles, (a.W + MOE_BN - 1) / MOE_BN), dim3(256), 0, s, a);
 }
 
-// Four launches: route, sort, the experts' first products with their activation,
-// their second products with the weights.
+// Three launches: route (with the ordering of the pairs), the experts' first products with
+// their activation, their second products with the weights.
 GB_EXPORT int gb_moe_forward_f32(const MoeArgs* a, cudaStream_t s) { return moe_forward<float>(*a, s); }
 GB_EXPORT int gb_moe_forward_bf16(const MoeArgs* a, cudaStream_t s) { return moe_forward<bf16>(*a, s); }

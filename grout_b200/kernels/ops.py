@@ -1472,7 +1472,7 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: torch.Tenso
     key = (dev.index or 0, E)
     counts = _MOE_COUNTS.get(key)      # zero between calls: the kernels leave it so
     if counts is None:
-        counts = _MOE_COUNTS[key] = torch.zeros((E,), dtype=torch.int32, device=dev)
+        counts = _MOE_COUNTS[key] = torch.zeros((E + 1,), dtype=torch.int32, device=dev)
     a = _MoeArgs()
     a.x, a.router_w, a.correction = x.data_ptr(), router_w.data_ptr(), correction.data_ptr()
     a.w_gate, a.w_up, a.w_down = w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr()
@@ -1481,7 +1481,7 @@ def moe_forward(x: torch.Tensor, router_w: torch.Tensor, correction: torch.Tenso
     a.T, a.W, a.F, a.E, a.n_identity, a.top = T, W, F, E, int(n_identity), int(top)
     a.n_groups, a.keep_groups, a.limit, a.slope = int(n_groups), int(keep_groups), float(limit), float(slope)
     _check(_fn("moe", f"gb_moe_forward_{_suffix(x.dtype)}", "pp")(ctypes.addressof(a), _stream()),
-           "moe_forward", 4)
+           "moe_forward", 3)
     return (out, ids, wts) if want_choice else out
 
 
