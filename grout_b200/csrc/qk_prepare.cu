@@ -236,7 +236,7 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       for (int p = 0; p < NP; ++p)
         ss += lo[p][0] * lo[p][0] + lo[p][1] * lo[p][1] + hi[p][0] * hi[p][0] + hi[p][1] * hi[p][1];
       ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
         // (beyond the head the values are zero and stay zero)
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(128, 8) qk_prepare_wide_kernel(const QkPrepare
 #pragma unroll
     for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (normed) {
-      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
       const float* wn = kind == 0 ? wq_s : wk_s;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -511,7 +511,7 @@ __global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareAr
       for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
       for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (wn) {
-        const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+        const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * to_f32<WT>(wn[j0 + e]);
       }
@@ -651,11 +651,11 @@ static int check(const QkPrepareArgs& a) {
   return 0;
 }
 
-// The kernels that keep a head in registers know one head size and no query
-// temperature; heads of two sizes, filled-up rows and the temperature take the
-// plain kernel.
+// The kernels that keep a head in registers know one head size, and the query
+// temperature as a factor of the query norm's; heads of two sizes, filled-up rows
+// and a temperature without a query norm take the plain kernel.
 static bool plain_only(const QkPrepareArgs& a) {
-  return (a.Dv > 0 && a.Dv != a.D) || (a.Ds > 0 && a.Ds != a.D) || a.q_temp_every > 0;
+  return (a.Dv > 0 && a.Dv != a.D) || (a.Ds > 0 && a.Ds != a.D) || (a.q_temp_every > 0 && !a.q_w);
 }
 
 GB_EXPORT int gb_qk_prepare_f32(const QkPrepareArgs* a, int w_is_f32, cudaStream_t s) {
