@@ -63,8 +63,8 @@ struct DeltaArgs {
   int n_tokens, n_seqs, H, G, dk, dv, taps;
   float unit_eps, norm_eps;
   int prep_stride;         // floats between rows of prep: round4(Cc + 2 H) + 48 H
-  int few_rows;            // no sequence brings more than DELTA_B rows (a decode step): the scan
-                           //   works out its one group's scalars itself and `gram` is not launched
+  int few_rows;            // 1: no sequence brings more than DELTA_B rows, 2: none more than one (a decode
+                           //   step): the scan works out its one group's scalars itself, `gram` is not launched
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -187,10 +187,18 @@ __host__ __device__ __forceinline__ int delta_gram_offset(int Cc, int H) { retur
 //   [44, 48) beta_j
 // Rows beyond the sequence's end are neutral (beta 0, g 1, products 0).
 #define DELTA_COEF 48
+// Where the pieces lie for groups of B rows (B = 4: the table above); the whole is filled up
+// to a multiple of four floats.
+template <int B> struct DeltaCoef {
+  static constexpr int A = 0, C = B, CUM = B + B * B, D = 2 * B + B * B, E = 2 * B + 2 * B * B,
+                       BETA = 3 * B + 2 * B * B, SIZE = (4 * B + 2 * B * B + 3) / 4 * 4;
+};
+static_assert(DeltaCoef<DELTA_B>::SIZE == DELTA_COEF, "the scalars of a group of four rows are 48 floats");
+
+template <int B>
 __device__ __forceinline__ void delta_group_scalars(float* out, const float* dots,
-                                                    const float (&beta)[DELTA_B],
-                                                    const float (&g)[DELTA_B]) {
-  constexpr int B = DELTA_B;
+                                                    const float (&beta)[B], const float (&g)[B]) {
+  using L = DeltaCoef<B>;
   float quot[B][B], cum[B + 1];
   cum[0] = 1.f;
   for (int j = 0; j < B; ++j) {
@@ -199,13 +207,13 @@ __device__ __forceinline__ void delta_group_scalars(float* out, const float* dot
     for (int i = 0; i < j; ++i) quot[i][j] = quot[i][j - 1] * g[j];
   }
   for (int j = 0; j < B; ++j) {
-    out[j] = beta[j] * g[j] * cum[j];
-    out[20 + j] = cum[j + 1];
-    out[40 + j] = quot[j][B - 1];
-    out[44 + j] = beta[j];
+    out[L::A + j] = beta[j] * g[j] * cum[j];
+    out[L::CUM + j] = cum[j + 1];
+    out[L::E + j] = quot[j][B - 1];
+    out[L::BETA + j] = beta[j];
     for (int i = 0; i < B; ++i) {
-      out[4 + i * B + j] = i < j ? beta[j] * g[j] * quot[i][j - 1] * dots[i * B + j] : 0.f;
-      out[24 + i * B + j] = i <= j ? quot[i][j] * dots[B * B + i * B + j] : 0.f;
+      out[L::C + i * B + j] = i < j ? beta[j] * g[j] * quot[i][j - 1] * dots[i * B + j] : 0.f;
+      out[L::D + i * B + j] = i <= j ? quot[i][j] * dots[B * B + i * B + j] : 0.f;
     }
   }
 }
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(128) delta_gram_kernel(const DeltaArgs a) {
       beta[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + h] : 0.f;
       g[j] = j < nb ? a.prep[(size_t)(t + j) * P + Cc + H + h] : 1.f;
     }
-    delta_group_scalars(a.prep + (size_t)t * P + delta_gram_offset(Cc, H) + h * DELTA_COEF, dots, beta, g);
+    delta_group_scalars<DELTA_B>(a.prep + (size_t)t * P + delta_gram_offset(Cc, H) + h * DELTA_COEF, dots, beta, g);
   }
   pdl_launch_dependents_if_large();
 }
@@ -253,14 +261,17 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 // R floats of a column per lane, in pieces of four: piece i of lane l holds the
 // elements (i * 8 + l) * 4 .. + 3, so that the lanes of a column read contiguous
 // bytes of shared memory, and of the state, at a time.
-template <int R>
+// B = 4 rows a turn; B = 1 for a step in which every sequence brings one row (a decode step):
+// one staged row, one group, far fewer registers, so that more of its many short blocks fit an SM.
+template <int R, int B>
 __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(const DeltaArgs a) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int B = DELTA_B;
+  using L = DeltaCoef<B>;
+  constexpr int TT = B == 1 ? 1 : DELTA_TT;            // rows of a stage
   constexpr int DKP = DELTA_LANES * R;                       // dk filled up with zeros
-  constexpr int GRAM = DELTA_COEF;
+  constexpr int GRAM = L::SIZE;
   // q | k | v | the groups' scalars
-  constexpr int STAGE = DELTA_TT * (2 * DKP + DELTA_COLS) + (DELTA_TT / B) * GRAM;
+  constexpr int STAGE = TT * (2 * DKP + DELTA_COLS) + (TT / B) * GRAM;
   pdl_launch_dependents_if_small();
   const int seq = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
   const int col0 = blockIdx.x * DELTA_COLS;
@@ -298,21 +309,21 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
   const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   auto stage_in = [&](int chunk, int st) {
     float* base = sm + st * STAGE;
-    float* vs = base + 2 * DELTA_TT * DKP;
-    float* gr = vs + DELTA_TT * DELTA_COLS;
-    const int t0 = row0 + chunk * DELTA_TT;
-    const int nt = min(DELTA_TT, row0 + n - t0);
+    float* vs = base + 2 * TT * DKP;
+    float* gr = vs + TT * DELTA_COLS;
+    const int t0 = row0 + chunk * TT;
+    const int nt = min(TT, row0 + n - t0);
     for (int tt = warp; tt < nt; tt += nwarps) {          // a warp per token: its q, its k, its values
       const float* src = a.prep + (size_t)(t0 + tt) * P;
       if (wide) {
         for (int pc = lane; pc < dk / 4; pc += 32) {
           cp_async16(base + tt * DKP + pc * 4, src + kvh * dk + pc * 4, true);
-          cp_async16(base + (DELTA_TT + tt) * DKP + pc * 4, src + (G + kvh) * dk + pc * 4, true);
+          cp_async16(base + (TT + tt) * DKP + pc * 4, src + (G + kvh) * dk + pc * 4, true);
         }
       } else {
         for (int d = lane; d < dk; d += 32) {
           cp_async4(base + tt * DKP + d, src + kvh * dk + d);
-          cp_async4(base + (DELTA_TT + tt) * DKP + d, src + (G + kvh) * dk + d);
+          cp_async4(base + (TT + tt) * DKP + d, src + (G + kvh) * dk + d);
         }
       }
       if (lane < DELTA_COLS && col0 + lane < dv)
@@ -327,12 +338,12 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     if (fill > 0) {
       for (int i = tid; i < fill * DKP; i += blockDim.x) {
         base[nt * DKP + i] = 0.f;
-        base[(DELTA_TT + nt) * DKP + i] = 0.f;
+        base[(TT + nt) * DKP + i] = 0.f;
       }
       for (int i = tid; i < fill * DELTA_COLS; i += blockDim.x) vs[nt * DELTA_COLS + i] = 0.f;
     }
   };
-  const int n_chunks = (n + DELTA_TT - 1) / DELTA_TT;
+  const int n_chunks = (n + TT - 1) / TT;
   float beta_f[B], g_f[B];      // a step of few rows: the one group's beta and g, asked for early
 #pragma unroll
   for (int j = 0; j < B; ++j) {
@@ -353,18 +364,18 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
     }
     __syncthreads();
     const float* base = sm + st * STAGE;
-    const float* vs = base + 2 * DELTA_TT * DKP;
-    const float* gr = vs + DELTA_TT * DELTA_COLS;
-    const int t0 = row0 + c * DELTA_TT;
-    const int nt = min(DELTA_TT, row0 + n - t0);
+    const float* vs = base + 2 * TT * DKP;
+    const float* gr = vs + TT * DELTA_COLS;
+    const int t0 = row0 + c * TT;
+    const int nt = min(TT, row0 + n - t0);
     if (a.few_rows) {       // the one group's products from the staged rows, then its scalars
-      __shared__ float dots[2 * DELTA_B * DELTA_B];
+      __shared__ float dots[2 * B * B];
       for (int e = warp; e < 2 * B * B; e += nwarps) {
         const int with_q = e / (B * B), i = (e % (B * B)) / B, j = e % B;
         float acc = 0.f;
         if (i < nt && j < nt && (with_q ? i <= j : i < j)) {
-          const float* ki = base + (DELTA_TT + i) * DKP;
-          const float* xj = base + (with_q ? j : DELTA_TT + j) * DKP;
+          const float* ki = base + (TT + i) * DKP;
+          const float* xj = base + (with_q ? j : TT + j) * DKP;
           for (int d = lane; d < dk; d += 32) acc = fmaf(ki[d], xj[d], acc);
           acc = warp_sum(acc);
         }
@@ -372,7 +383,7 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
       }
       __syncthreads();
       if (tid == 0)
-        delta_group_scalars(sm + st * STAGE + 2 * DELTA_TT * DKP + DELTA_TT * DELTA_COLS, dots, beta_f, g_f);
+        delta_group_scalars<B>(sm + st * STAGE + 2 * TT * DKP + TT * DELTA_COLS, dots, beta_f, g_f);
       __syncthreads();
     }
     for (int g0 = 0; g0 < nt; g0 += B) {
@@ -380,7 +391,7 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
 #pragma unroll
       for (int j = 0; j < B; ++j) {
         const float4* qp = reinterpret_cast<const float4*>(base + (g0 + j) * DKP) + l;
-        const float4* kp = reinterpret_cast<const float4*>(base + (DELTA_TT + g0 + j) * DKP) + l;
+        const float4* kp = reinterpret_cast<const float4*>(base + (TT + g0 + j) * DKP) + l;
         float d1 = 0.f, d2 = 0.f;
 #pragma unroll
         for (int i = 0; i < R / 4; ++i) {
@@ -412,18 +423,18 @@ __global__ void __launch_bounds__(DELTA_LANES * DELTA_COLS) delta_scan_kernel(co
 #pragma unroll
       for (int j = 0; j < B; ++j) {
         const float v = vs[(g0 + j) * DELTA_COLS + (tid / DELTA_LANES)];
-        float uj = fmaf(co[44 + j], v, -co[j] * sk[j]);
+        float uj = fmaf(co[L::BETA + j], v, -co[L::A + j] * sk[j]);
 #pragma unroll
-        for (int i = 0; i < j; ++i) uj = fmaf(-co[4 + i * B + j], u[i], uj);
+        for (int i = 0; i < j; ++i) uj = fmaf(-co[L::C + i * B + j], u[i], uj);
         u[j] = uj;
-        float o = co[20 + j] * sq[j];
+        float o = co[L::CUM + j] * sq[j];
 #pragma unroll
-        for (int i = 0; i <= j; ++i) o = fmaf(co[24 + i * B + j], u[i], o);
+        for (int i = 0; i <= j; ++i) o = fmaf(co[L::D + i * B + j], u[i], o);
         if (l == 0 && active && g0 + j < nt) a.o[((size_t)(t0 + g0 + j) * H + h) * dv + col] = o;
       }
 #pragma unroll
-      for (int i = 0; i < B; ++i) w[i] = co[40 + i] * u[i];
-      const float cum = co[20 + B - 1];
+      for (int i = 0; i < B; ++i) w[i] = co[L::E + i] * u[i];
+      const float cum = co[L::CUM + B - 1];
 #pragma unroll
       for (int x = 0; x < R; ++x) {
         float sx = cum * S[x];
@@ -477,17 +488,23 @@ __global__ void delta_finish_kernel(const DeltaArgs a) {
   pdl_launch_dependents_if_large();
 }
 
-template <int R>
-static int scan_launch(const DeltaArgs& a, cudaStream_t s) {
+template <int R, int B>
+static int scan_launch_b(const DeltaArgs& a, cudaStream_t s) {
   const dim3 grid((a.dv + DELTA_COLS - 1) / DELTA_COLS, a.H, a.n_seqs), block(DELTA_LANES * DELTA_COLS);
-  const size_t smem = (size_t)(a.few_rows ? 1 : 2) * (DELTA_TT * (2 * DELTA_LANES * R + DELTA_COLS) +
-                                                      (DELTA_TT / DELTA_B) * DELTA_COEF) * sizeof(float);
+  constexpr int TT = B == 1 ? 1 : DELTA_TT;
+  const size_t smem = (size_t)(a.few_rows ? 1 : 2) * (TT * (2 * DELTA_LANES * R + DELTA_COLS) +
+                                                      (TT / B) * DeltaCoef<B>::SIZE) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaError_t ce = cudaFuncSetAttribute(delta_scan_kernel<R>,
+    cudaError_t ce = cudaFuncSetAttribute(delta_scan_kernel<R, B>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
   }
-  return gb_launch(delta_scan_kernel<R>, grid, block, smem, s, a);
+  return gb_launch(delta_scan_kernel<R, B>, grid, block, smem, s, a);
+}
+
+template <int R>
+static int scan_launch(const DeltaArgs& a, cudaStream_t s) {
+  return a.few_rows == 2 ? scan_launch_b<R, 1>(a, s) : scan_launch_b<R, DELTA_B>(a, s);
 }
 
 static int delta_check(const DeltaArgs& a) {

@@ -1413,7 +1413,7 @@ def delta_forward(proj: torch.Tensor, state: torch.Tensor, conv_w: torch.Tensor,
     a.prep, a.o, a.y = prep.data_ptr(), o.data_ptr(), y.data_ptr()
     a.n_tokens, a.n_seqs, a.H, a.G, a.dk, a.dv, a.taps = T, n_seqs, H, G, dk, dv, taps
     a.unit_eps, a.norm_eps, a.prep_stride = float(unit_eps), float(norm_eps), prep_stride
-    a.few_rows = int(max_rows is not None and 0 < max_rows <= 4)
+    a.few_rows = 0 if max_rows is None or not 0 < max_rows <= 4 else (2 if max_rows == 1 else 1)
     _check(_fn("delta", f"gb_delta_forward_{_suffix(dtype)}", "pp")(ctypes.addressof(a), _stream()),
            "delta_forward", 3 if a.few_rows else 4)
     return y
