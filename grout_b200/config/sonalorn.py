@@ -3,7 +3,8 @@
 The file names the design under ``architecture`` and describes the model layer
 by layer: ``layers`` is a list of objects ``{"type", "mixer", "mlp"}`` (``mlp``
 null: the layer has no feed-forward).  A layer with ``weights_of: j`` has no
-tensors of its own and runs layer j's, on a cache or state of its own.  Nothing
+tensors of its own and runs layer j's (its sizes and constants are layer j's), on
+a cache or state of its own.  Nothing
 that the arithmetic needs is defaulted: a constant that is absent stands for a
 term that is absent (no ``q_temp``: queries are not scaled by position; no
 ``groups``: every expert can be chosen).
@@ -74,10 +75,8 @@ class SonalornConfig(ModelConfig):
             if not _count(src) or src >= len(self.layers) or src == i or \
                     not isinstance(self.layers[src], dict) or "weights_of" in self.layers[src]:
                 yield f"{where}.weights_of={src!r} must name another layer that has tensors of its own"
-            else:
-                mine = {k: v for k, v in layer.items() if k != "weights_of"}
-                if mine != dict(self.layers[src]):
-                    yield f"{where} uses the weights of layer {src} but is described differently"
+            elif layer["type"] != self.layers[src].get("type"):
+                yield f"{where} uses the weights of layer {src}, which is of another type"
             return
         m = layer.get("mixer")
         if not isinstance(m, dict):

@@ -34,9 +34,10 @@ struct QkPrepareArgs {
 };
 
 __device__ __forceinline__ float query_temperature(const QkPrepareArgs& a, int pos) {
-  return a.q_temp_every > 0
-             ? 1.0f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every + 1))
-             : 1.0f;
+  float t = 1.0f;
+  if (a.q_temp_every > 0)     // the same for every thread of the kernel: a branch, not a select
+    t = 1.0f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every + 1));
+  return t;
 }
 
 template <typename T, typename WT>
@@ -190,6 +191,7 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       wk[p][e] = (j < HALF && a.k_w) ? to_f32<WT>(((const WT*)a.k_w)[idx]) : 1.f;
     }
   }
+  const float q_temp = query_temperature(a, pos);   // the position was there before the step: off the path
   pdl_wait();
   // heads of this token in turn: few blocks per token when there are many tokens
   for (int head = blockIdx.y * warps + warp; head < n_heads; head += gridDim.y * warps) {
@@ -236,7 +238,7 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       for (int p = 0; p < NP; ++p)
         ss += lo[p][0] * lo[p][0] + lo[p][1] * lo[p][1] + hi[p][0] * hi[p][0] + hi[p][1] * hi[p][1];
       ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? q_temp : 1.0f);
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
         // (beyond the head the values are zero and stay zero)
@@ -328,6 +330,7 @@ __global__ void __launch_bounds__(128, 8) qk_prepare_wide_kernel(const QkPrepare
       paged = true;
     }
   }
+  const float q_temp = query_temperature(a, pos);   // the position was there before the step: off the path
   pdl_wait();
   const int passes = (n_heads + HPW - 1) / HPW;
   // A warp's passes in groups of WIDE_U: the loads of a group are all requested before the
@@ -371,7 +374,7 @@ __global__ void __launch_bounds__(128, 8) qk_prepare_wide_kernel(const QkPrepare
 #pragma unroll
     for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (normed) {
-      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? q_temp : 1.0f);
       const float* wn = kind == 0 ? wq_s : wk_s;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -469,6 +472,7 @@ __global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareAr
     cs[e] = role ? sc_s[half + (j0 + e) % half] : 1.f;
     if (role == 1) sn[e] = -sn[e];               // x cos - partner sin; the second: x cos + partner sin
   }
+  const float q_temp = query_temperature(a, pos);   // the position was there before the step: off the path
   pdl_wait();
   const int passes = (n_heads + HPW - 1) / HPW;
   for (int pass = blockIdx.y * warps + warp; pass < passes; pass += gridDim.y * warps) {
@@ -511,7 +515,7 @@ __global__ void __launch_bounds__(128) qk_prepare_chunk_kernel(const QkPrepareAr
       for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
       for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (wn) {
-        const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? query_temperature(a, pos) : 1.0f);
+        const float inv = 1.0f / sqrtf(ss / (float)D + a.eps) * (kind == 0 ? q_temp : 1.0f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * to_f32<WT>(wn[j0 + e]);
       }
